@@ -1,0 +1,397 @@
+// C ABI of libfswiglu.so (declared in include/fswiglu.h): argument checks,
+// TMA tensor-map encoding, tile rasterisation choices and kernel launches.
+// No torch types and no allocation on the hot path; the only device memory
+// this file owns is one 256-byte status block per device.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdint>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/fswiglu.h"
+#include "decode_sm100.cuh"
+#include "gemm_sm100.cuh"
+
+namespace {
+
+using namespace fsw;
+
+constexpr int kMaxDevices = 64;
+
+constexpr int kMaxHostSlabs = 64;
+
+struct DeviceState {
+  bool ready = false;
+  int num_sms = 0;
+  uint32_t* status = nullptr;  // device memory, 64 words
+  // Lazily created by the host-buffer entry point only.
+  bool host_ready = false;
+  cudaStream_t h2d_stream = nullptr;
+  cudaStream_t d2h_stream = nullptr;
+  cudaEvent_t ev_start = nullptr;
+  cudaEvent_t ev_h2d[kMaxHostSlabs] = {};
+  cudaEvent_t ev_done[kMaxHostSlabs] = {};
+};
+
+std::mutex g_mutex;
+DeviceState g_dev[kMaxDevices];
+std::atomic<uint64_t> g_launches{0};
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+template <typename Kernel>
+cudaError_t opt_in_smem(Kernel k, int bytes) {
+  return cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+}
+
+// One-time per-device set-up: capability check, status block, shared-memory opt-in.
+int device_state(DeviceState** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return FSWIGLU_ERR_NO_DEVICE;
+  if (dev < 0 || dev >= kMaxDevices) return FSWIGLU_ERR_NO_DEVICE;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceState& st = g_dev[dev];
+  if (!st.ready) {
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return FSWIGLU_ERR_NO_DEVICE;
+    if (prop.major != 10) return FSWIGLU_ERR_NO_DEVICE;
+    st.num_sms = prop.multiProcessorCount;
+    if (g_encode == nullptr) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult q;
+      if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) !=
+              cudaSuccess ||
+          fn == nullptr) {
+        return FSWIGLU_ERR_CUDA;
+      }
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    if (cudaMalloc(&st.status, 256) != cudaSuccess) return FSWIGLU_ERR_CUDA;
+    if (cudaMemset(st.status, 0, 256) != cudaSuccess) return FSWIGLU_ERR_CUDA;
+    cudaError_t e = cudaSuccess;
+    e = e ? e : opt_in_smem(gemm_tcgen05_kernel<kPlain, false>, kGemmSmemBytes);
+    e = e ? e : opt_in_smem(gemm_tcgen05_kernel<kPlain, true>, kGemmSmemBytes);
+    e = e ? e : opt_in_smem(gemm_tcgen05_kernel<kGatedSplit, false>, kGemmSmemBytes);
+    e = e ? e : opt_in_smem(gemm_tcgen05_kernel<kGatedInterleaved, false>, kGemmSmemBytes);
+    e = e ? e : decode_opt_in_smem();
+    if (e != cudaSuccess) return FSWIGLU_ERR_CUDA;
+    st.ready = true;
+  }
+  *out = &st;
+  return FSWIGLU_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Tensor map over a row-major bf16 matrix [rows, cols] with pitch `ld` elements; one box is
+// 64 columns (128 bytes, the swizzle width) x box_rows rows.
+int encode_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld,
+               uint32_t box_rows) {
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2u};
+  const cuuint32_t box[2] = {64u, box_rows};
+  const cuuint32_t elem_strides[2] = {1u, 1u};
+  const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
+                              strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
+}
+
+int check_matrix(const void* p, int64_t rows, int64_t cols, int64_t ld, bool tma_read) {
+  if (p == nullptr) return FSWIGLU_ERR_BAD_ARG;
+  if (rows < 0 || cols <= 0) return FSWIGLU_ERR_BAD_ARG;
+  if (rows > 0x7fffffffll || cols > 0x7fffffffll) return FSWIGLU_ERR_SHAPE;
+  if (ld < cols) return FSWIGLU_ERR_SHAPE;
+  if (tma_read) {
+    if (cols % 8 != 0) return FSWIGLU_ERR_SHAPE;
+    if (!aligned16(p) || ld % 8 != 0) return FSWIGLU_ERR_ALIGNMENT;
+  }
+  return FSWIGLU_OK;
+}
+
+// How many 128-row M-tiles share one sweep over N: sized so that the slab of A they
+// cover (group_m * 128 rows * K bf16) stays comfortably inside the 126 MB L2.
+int pick_group_m(int num_m_tiles, int64_t K) {
+  const int64_t slab_budget = 32ll << 20;
+  int64_t g = slab_budget / (128 * K * 2);
+  if (g < 1) g = 1;
+  if (g > num_m_tiles) g = num_m_tiles;
+  return static_cast<int>(g);
+}
+
+template <int kMode, bool kOutF32>
+int launch_gemm(const DeviceState& st, const CUtensorMap& ma, const CUtensorMap& mb0,
+                const CUtensorMap& mb1, const GemmParams& p, cudaStream_t stream) {
+  const int tiles = p.num_m_tiles * p.num_n_tiles;
+  const int grid = tiles < st.num_sms ? tiles : st.num_sms;
+  gemm_tcgen05_kernel<kMode, kOutF32><<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(ma, mb0, mb1, p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
+}
+
+int gateup_impl(DeviceState& st, const void* x, int64_t ldx, const void* w0, int64_t ldw,
+                const void* w_up, void* h, int64_t ldh, int64_t M, int64_t F, int64_t d,
+                int interleaved, cudaStream_t stream) {
+  int rc;
+  if ((rc = check_matrix(x, M, d, ldx, true))) return rc;
+  if (interleaved) {
+    if (w_up != nullptr) return FSWIGLU_ERR_BAD_ARG;
+    if ((rc = check_matrix(w0, 2 * F, d, ldw, true))) return rc;
+  } else {
+    if ((rc = check_matrix(w0, F, d, ldw, true))) return rc;
+    if ((rc = check_matrix(w_up, F, d, ldw, true))) return rc;
+  }
+  if ((rc = check_matrix(h, M, F, ldh, false))) return rc;
+  if (M == 0) return FSWIGLU_OK;
+
+  CUtensorMap ma, mb0, mb1;
+  if ((rc = encode_map(&ma, x, M, d, ldx, 128))) return rc;
+  if (interleaved) {
+    if ((rc = encode_map(&mb0, w0, 2 * F, d, ldw, 128))) return rc;
+    mb1 = mb0;
+  } else {
+    if ((rc = encode_map(&mb0, w0, F, d, ldw, 128))) return rc;
+    if ((rc = encode_map(&mb1, w_up, F, d, ldw, 128))) return rc;
+  }
+  GemmParams p;
+  p.out = h;
+  p.ld_out = ldh;
+  p.M = static_cast<int>(M);
+  p.n_out = static_cast<int>(F);
+  p.K = static_cast<int>(d);
+  p.num_m_tiles = static_cast<int>((M + 127) / 128);
+  p.num_n_tiles = static_cast<int>((F + 127) / 128);
+  p.group_m = pick_group_m(p.num_m_tiles, d);
+  p.vec_ok = (aligned16(h) && ldh % 8 == 0) ? 1 : 0;
+  p.status = st.status;
+  return interleaved ? launch_gemm<kGatedInterleaved, false>(st, ma, mb0, mb1, p, stream)
+                     : launch_gemm<kGatedSplit, false>(st, ma, mb0, mb1, p, stream);
+}
+
+int down_impl(DeviceState& st, const void* h, int64_t ldh, const void* w_down, int64_t ldw, void* out,
+              int64_t ldo, int64_t M, int64_t d, int64_t F, int out_dtype, cudaStream_t stream) {
+  int rc;
+  if (out_dtype != FSWIGLU_OUT_BF16 && out_dtype != FSWIGLU_OUT_F32) return FSWIGLU_ERR_BAD_ARG;
+  if ((rc = check_matrix(h, M, F, ldh, true))) return rc;
+  if ((rc = check_matrix(w_down, d, F, ldw, true))) return rc;
+  if ((rc = check_matrix(out, M, d, ldo, false))) return rc;
+  if (M == 0) return FSWIGLU_OK;
+
+  CUtensorMap ma, mb;
+  if ((rc = encode_map(&ma, h, M, F, ldh, 128))) return rc;
+  if ((rc = encode_map(&mb, w_down, d, F, ldw, 128))) return rc;
+  GemmParams p;
+  p.out = out;
+  p.ld_out = ldo;
+  p.M = static_cast<int>(M);
+  p.n_out = static_cast<int>(d);
+  p.K = static_cast<int>(F);
+  p.num_m_tiles = static_cast<int>((M + 127) / 128);
+  p.num_n_tiles = static_cast<int>((d + 255) / 256);
+  p.group_m = pick_group_m(p.num_m_tiles, F);
+  const bool f32 = out_dtype == FSWIGLU_OUT_F32;
+  p.vec_ok = (aligned16(out) && ldo % (f32 ? 4 : 8) == 0) ? 1 : 0;
+  p.status = st.status;
+  return f32 ? launch_gemm<kPlain, true>(st, ma, mb, mb, p, stream)
+             : launch_gemm<kPlain, false>(st, ma, mb, mb, p, stream);
+}
+
+size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+
+extern "C" {
+
+int fswiglu_gateup_bf16(const void* x, int64_t ldx, const void* w_gate_or_w13, int64_t ldw,
+                        const void* w_up, void* h, int64_t ldh, int64_t M, int64_t F, int64_t d,
+                        int interleaved, void* stream) {
+  if (M < 0 || F <= 0 || d <= 0) return FSWIGLU_ERR_BAD_ARG;
+  DeviceState* st = nullptr;
+  if (int rc = device_state(&st)) return rc;
+  return gateup_impl(*st, x, ldx, w_gate_or_w13, ldw, w_up, h, ldh, M, F, d, interleaved,
+                     static_cast<cudaStream_t>(stream));
+}
+
+int fswiglu_down_bf16(const void* h, int64_t ldh, const void* w_down, int64_t ldw, void* out,
+                      int64_t ldo, int64_t M, int64_t d, int64_t F, int out_dtype, void* stream) {
+  if (M < 0 || F <= 0 || d <= 0) return FSWIGLU_ERR_BAD_ARG;
+  DeviceState* st = nullptr;
+  if (int rc = device_state(&st)) return rc;
+  return down_impl(*st, h, ldh, w_down, ldw, out, ldo, M, d, F, out_dtype,
+                   static_cast<cudaStream_t>(stream));
+}
+
+size_t fswiglu_workspace_bytes(int64_t M, int64_t d, int64_t F) {
+  if (M <= 0 || d <= 0 || F <= 0) return 0;
+  size_t bytes = round_up(static_cast<size_t>(M) * static_cast<size_t>(F) * 2u, 256);
+  if (M <= kDecodeMaxTokens) bytes += decode_workspace_bytes(M, d, F);
+  return bytes;
+}
+
+int fswiglu_mlp_bf16(const void* x, int64_t ldx, const void* w_gate, const void* w_up, int64_t ldw_gu,
+                     const void* w_down, int64_t ldw_d, void* out, int64_t ldo, int out_dtype,
+                     int64_t M, int64_t d, int64_t F, void* workspace, size_t workspace_bytes,
+                     void* stream) {
+  if (M < 0 || F <= 0 || d <= 0) return FSWIGLU_ERR_BAD_ARG;
+  if (M == 0) return FSWIGLU_OK;
+  DeviceState* st = nullptr;
+  if (int rc = device_state(&st)) return rc;
+  if (workspace == nullptr || workspace_bytes < fswiglu_workspace_bytes(M, d, F) ||
+      (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) {
+    return FSWIGLU_ERR_WORKSPACE;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  void* h = workspace;
+  if (M <= kDecodeMaxTokens && decode_supported(M, d, F, ldx, ldw_gu, ldw_d)) {
+    if (out_dtype != FSWIGLU_OUT_BF16 && out_dtype != FSWIGLU_OUT_F32) return FSWIGLU_ERR_BAD_ARG;
+    if (x == nullptr || w_gate == nullptr || w_up == nullptr || w_down == nullptr || out == nullptr)
+      return FSWIGLU_ERR_BAD_ARG;
+    if (ldo < d) return FSWIGLU_ERR_SHAPE;
+    void* partials = static_cast<uint8_t*>(workspace) +
+                     round_up(static_cast<size_t>(M) * static_cast<size_t>(F) * 2u, 256);
+    int launches = 0;
+    const cudaError_t e =
+        decode_mlp_launch(x, ldx, w_gate, w_up, ldw_gu, w_down, ldw_d, out, ldo, out_dtype, M, d, F, h,
+                          partials, st->num_sms, st->status, s, &launches);
+    g_launches.fetch_add(static_cast<uint64_t>(launches), std::memory_order_relaxed);
+    return e == cudaSuccess ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
+  }
+  if (int rc = gateup_impl(*st, x, ldx, w_gate, ldw_gu, w_up, h, F, M, F, d, 0, s)) return rc;
+  return down_impl(*st, h, F, w_down, ldw_d, out, ldo, M, d, F, out_dtype, s);
+}
+
+namespace {
+
+// Rows per slab of the host-buffer pipeline: large enough that each slab still fills the
+// machine (>= 1024 rows), small enough that the first copy in and the last copy out are short.
+int64_t host_slab_rows(int64_t M) {
+  int64_t rows = 1024;
+  const int64_t min_rows = (M + kMaxHostSlabs - 1) / kMaxHostSlabs;
+  if (rows < min_rows) rows = (min_rows + 127) / 128 * 128;
+  if (rows > M) rows = M;
+  return rows;
+}
+
+int host_state(DeviceState& st) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (st.host_ready) return FSWIGLU_OK;
+  if (cudaStreamCreateWithFlags(&st.h2d_stream, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaStreamCreateWithFlags(&st.d2h_stream, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaEventCreateWithFlags(&st.ev_start, cudaEventDisableTiming) != cudaSuccess) {
+    return FSWIGLU_ERR_CUDA;
+  }
+  for (int i = 0; i < kMaxHostSlabs; ++i) {
+    if (cudaEventCreateWithFlags(&st.ev_h2d[i], cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&st.ev_done[i], cudaEventDisableTiming) != cudaSuccess) {
+      return FSWIGLU_ERR_CUDA;
+    }
+  }
+  st.host_ready = true;
+  return FSWIGLU_OK;
+}
+
+}  // namespace
+
+size_t fswiglu_host_workspace_bytes(int64_t M, int64_t d, int64_t F) {
+  if (M <= 0 || d <= 0 || F <= 0) return 0;
+  const size_t act = round_up(static_cast<size_t>(M) * static_cast<size_t>(d) * 2u, 256);
+  return 2 * act + round_up(fswiglu_workspace_bytes(host_slab_rows(M), d, F), 256);
+}
+
+int fswiglu_mlp_bf16_host(const void* x_host, const void* w_gate, const void* w_up,
+                          const void* w_down, void* out_host, int64_t M, int64_t d, int64_t F,
+                          void* workspace, size_t workspace_bytes, void* stream) {
+  if (M < 0 || F <= 0 || d <= 0) return FSWIGLU_ERR_BAD_ARG;
+  if (M == 0) return FSWIGLU_OK;
+  if (x_host == nullptr || out_host == nullptr) return FSWIGLU_ERR_BAD_ARG;
+  DeviceState* st = nullptr;
+  if (int rc = device_state(&st)) return rc;
+  if (int rc = host_state(*st)) return rc;
+  if (workspace == nullptr || workspace_bytes < fswiglu_host_workspace_bytes(M, d, F) ||
+      (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) {
+    return FSWIGLU_ERR_WORKSPACE;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t act = round_up(static_cast<size_t>(M) * static_cast<size_t>(d) * 2u, 256);
+  uint8_t* x_dev = static_cast<uint8_t*>(workspace);
+  uint8_t* out_dev = x_dev + act;
+  uint8_t* mlp_ws = out_dev + act;
+  const int64_t slab = host_slab_rows(M);
+  const size_t mlp_ws_bytes = fswiglu_workspace_bytes(slab, d, F);
+  const int num_slabs = static_cast<int>((M + slab - 1) / slab);
+  const size_t row_bytes = static_cast<size_t>(d) * 2u;
+
+  bool ok = cudaEventRecord(st->ev_start, s) == cudaSuccess &&
+            cudaStreamWaitEvent(st->h2d_stream, st->ev_start, 0) == cudaSuccess &&
+            cudaStreamWaitEvent(st->d2h_stream, st->ev_start, 0) == cudaSuccess;
+  for (int i = 0; i < num_slabs && ok; ++i) {
+    const int64_t r0 = i * slab;
+    const int64_t rows = (M - r0 < slab) ? (M - r0) : slab;
+    ok = cudaMemcpyAsync(x_dev + r0 * row_bytes, static_cast<const uint8_t*>(x_host) + r0 * row_bytes,
+                         rows * row_bytes, cudaMemcpyHostToDevice, st->h2d_stream) == cudaSuccess &&
+         cudaEventRecord(st->ev_h2d[i], st->h2d_stream) == cudaSuccess;
+  }
+  int rc = FSWIGLU_OK;
+  for (int i = 0; i < num_slabs && ok && rc == FSWIGLU_OK; ++i) {
+    const int64_t r0 = i * slab;
+    const int64_t rows = (M - r0 < slab) ? (M - r0) : slab;
+    ok = cudaStreamWaitEvent(s, st->ev_h2d[i], 0) == cudaSuccess;
+    if (!ok) break;
+    rc = fswiglu_mlp_bf16(x_dev + r0 * row_bytes, d, w_gate, w_up, d, w_down, F, out_dev + r0 * row_bytes,
+                          d, FSWIGLU_OUT_BF16, rows, d, F, mlp_ws, mlp_ws_bytes, s);
+    if (rc != FSWIGLU_OK) break;
+    ok = cudaEventRecord(st->ev_done[i], s) == cudaSuccess &&
+         cudaStreamWaitEvent(st->d2h_stream, st->ev_done[i], 0) == cudaSuccess &&
+         cudaMemcpyAsync(static_cast<uint8_t*>(out_host) + r0 * row_bytes, out_dev + r0 * row_bytes,
+                         rows * row_bytes, cudaMemcpyDeviceToHost, st->d2h_stream) == cudaSuccess;
+  }
+  // Always drain what was queued, also on the error paths: the caller owns the host buffers.
+  const bool drained = cudaStreamSynchronize(st->h2d_stream) == cudaSuccess &&
+                       cudaStreamSynchronize(s) == cudaSuccess &&
+                       cudaStreamSynchronize(st->d2h_stream) == cudaSuccess;
+  if (rc != FSWIGLU_OK) return rc;
+  return (ok && drained) ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
+}
+
+int fswiglu_device_status(uint32_t* status, void* stream) {
+  DeviceState* st = nullptr;
+  if (int rc = device_state(&st)) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  uint32_t word = 0;
+  if (cudaMemcpyAsync(&word, st->status, sizeof(word), cudaMemcpyDeviceToHost, s) != cudaSuccess)
+    return FSWIGLU_ERR_CUDA;
+  if (cudaStreamSynchronize(s) != cudaSuccess) return FSWIGLU_ERR_CUDA;
+  if (word != 0) {
+    if (cudaMemsetAsync(st->status, 0, sizeof(word), s) != cudaSuccess) return FSWIGLU_ERR_CUDA;
+    if (cudaStreamSynchronize(s) != cudaSuccess) return FSWIGLU_ERR_CUDA;
+  }
+  if (status != nullptr) *status = word;
+  return word == 0 ? FSWIGLU_OK : FSWIGLU_ERR_WATCHDOG;
+}
+
+const char* fswiglu_status_string(int status) {
+  switch (status) {
+    case FSWIGLU_OK: return "ok";
+    case FSWIGLU_ERR_BAD_ARG: return "bad argument (null pointer, negative size or unknown enum)";
+    case FSWIGLU_ERR_ALIGNMENT: return "pointer or leading dimension not 16-byte aligned";
+    case FSWIGLU_ERR_SHAPE: return "unsupported shape (d and F must be multiples of 8, ld >= row length)";
+    case FSWIGLU_ERR_CUDA: return "CUDA call or kernel launch failed";
+    case FSWIGLU_ERR_WATCHDOG: return "device-side wait exceeded its limit";
+    case FSWIGLU_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+    case FSWIGLU_ERR_NO_DEVICE: return "current device is not an sm_100 GPU";
+    default: return "unknown status";
+  }
+}
+
+const char* fswiglu_version(void) { return "0.1.0"; }
+
+uint64_t fswiglu_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+}  // extern "C"

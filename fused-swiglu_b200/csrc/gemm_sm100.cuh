@@ -1,0 +1,364 @@
+// Persistent, warp-specialised tcgen05 GEMM for the two prefill stages of the
+// SwiGLU MLP forward:
+//
+//   gate-up stage  h[M,F]   = silu(x Wg^T) * (x Wu^T)      (gated epilogue)
+//   down stage     out[M,d] = h Wd^T                        (plain epilogue)
+//
+// All operands are K-major ("TN"): A is [rows, K] row-major, B is [cols, K]
+// row-major, exactly the layout of x / W_gate / W_up / h / W_down, so one TMA
+// box of 64 bf16 x 128 rows with the 128-byte swizzle is a ready-made UMMA
+// operand.  One CTA per SM:
+//
+//   warp 0       TMA producer (one lane): fills a 4-deep ring of
+//                {A 128x64, B 256x64} stages, 48 KiB each
+//   warp 1       TMEM owner + MMA issuer (one lane): 4 x tcgen05.mma
+//                (M=128, N=256, K=16) per stage into one of two 256-column
+//                TMEM accumulators
+//   warps 2..5   epilogue: tcgen05.ld the finished accumulator (one thread
+//                per output row), apply SiLU(g)*u, round once to bf16, store
+//
+// The accumulator is double-buffered (2 x 256 of the 512 TMEM columns), so the
+// epilogue of tile t overlaps the main loop of tile t+1.
+//
+// The B tile always holds 256 rows.  What they are depends on the mode:
+//   kPlain             256 consecutive rows of W            -> 256 outputs
+//   kGatedSplit        128 rows of W_gate, then 128 of W_up -> 128 outputs
+//   kGatedInterleaved  256 consecutive rows of the reference's packed W1W3
+//                      (even row = up, odd row = gate; reference
+//                      csrc/SwiGLU/swiglu.cu:376-383)        -> 128 outputs
+//
+// Ragged edges cost nothing extra: TMA zero-fills out-of-range rows and
+// K-columns on load, and stores are predicated per row / column.
+#pragma once
+
+#include "ptx_sm100.cuh"
+
+namespace fsw {
+
+enum GemmMode : int { kPlain = 0, kGatedSplit = 1, kGatedInterleaved = 2 };
+
+constexpr int kBlockM = 128;
+constexpr int kUmmaN = 256;
+constexpr int kBlockK = 64;   // 64 bf16 = one 128-byte swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kStages = 4;
+constexpr int kATileBytes = kBlockM * kBlockK * 2;      // 16 KiB
+constexpr int kBHalfBytes = 128 * kBlockK * 2;          // 16 KiB (one TMA box)
+constexpr int kBTileBytes = 2 * kBHalfBytes;            // 32 KiB
+constexpr int kStageBytes = kATileBytes + kBTileBytes;  // 48 KiB
+constexpr int kTmemCols = 512;
+constexpr int kGemmThreads = 192;
+constexpr int kNumEpilogueThreads = 128;
+// ring + 1 KiB alignment slack + barriers / bookkeeping
+constexpr int kGemmSmemBytes = kStages * kStageBytes + 1024 + 256;
+
+struct GemmParams {
+  void* out;          // bf16 (or fp32 when kOutF32) [M, n_out], row stride ld_out elements
+  long long ld_out;
+  int M;
+  int n_out;          // number of output columns
+  int K;
+  int num_m_tiles;
+  int num_n_tiles;
+  int group_m;        // rasterisation: this many M-tiles share a sweep over N
+  int vec_ok;         // 1 when every row start of `out` is 16-byte aligned
+  uint32_t* status;   // device watchdog word (0 = healthy)
+};
+
+struct TileCoord {
+  int m_tile;
+  int n_tile;
+};
+
+// Grouped rasterisation: consecutive tile ids walk down `group_m` M-tiles
+// before moving to the next N-tile, so the CTAs running at the same time share
+// a few B tiles and a bounded slab of A that stays in L2.
+__device__ __forceinline__ TileCoord tile_coord(int tile, const GemmParams& p) {
+  const int per_group = p.group_m * p.num_n_tiles;
+  const int g = tile / per_group;
+  const int r = tile - g * per_group;
+  const int first_m = g * p.group_m;
+  const int gm = min(p.group_m, p.num_m_tiles - first_m);
+  TileCoord c;
+  c.n_tile = r / gm;
+  c.m_tile = first_m + (r - c.n_tile * gm);
+  return c;
+}
+
+template <bool kOutF32>
+__device__ __forceinline__ void store_chunk32(const GemmParams& p, int row, int col0,
+                                              const float (&v)[32]) {
+  // v holds 32 consecutive output columns of one row, starting at col0.
+  if (row >= p.M || col0 >= p.n_out) return;
+  const int valid = min(32, p.n_out - col0);
+  if constexpr (kOutF32) {
+    float* dst = reinterpret_cast<float*>(p.out) + static_cast<long long>(row) * p.ld_out + col0;
+    if (p.vec_ok && valid == 32) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        if (i < valid) dst[i] = v[i];
+      }
+    }
+  } else {
+    __nv_bfloat16* dst =
+        reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(row) * p.ld_out + col0;
+    if (p.vec_ok && valid == 32) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint4 q;
+        q.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
+        q.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
+        q.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
+        q.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
+        reinterpret_cast<uint4*>(dst)[i] = q;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        if (i < valid) dst[i] = __float2bfloat16_rn(v[i]);
+      }
+    }
+  }
+}
+
+template <int kMode, bool kOutF32>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
+                    const __grid_constant__ CUtensorMap map_b0,
+                    const __grid_constant__ CUtensorMap map_b1, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // The 128-byte swizzle pattern repeats every 1024 bytes: tiles must start on that boundary.
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + kStages * kStageBytes;
+  // barrier block: full[4], empty[4], tmem_full[2], tmem_empty[2], drain, tmem ptr, abort flag
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+  const uint32_t drain_bar = bar_base + 8u * (2 * kStages + 4);
+  uint8_t* generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
+  volatile uint32_t* tmem_ptr_slot =
+      reinterpret_cast<volatile uint32_t*>(generic_base + kStages * kStageBytes + 8 * (2 * kStages + 5));
+  volatile uint32_t* abort_flag = tmem_ptr_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const uint32_t lane = lane_id();
+  const Watchdog wd{abort_flag, p.status};
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), kNumEpilogueThreads);
+    }
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_b0);
+    prefetch_tensormap(&map_b1);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr_slot;
+
+  const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+  const int num_kb = (p.K + kBlockK - 1) / kBlockK;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t issued_mask = 0, last_parity_mask = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+        const TileCoord tc = tile_coord(tile, p);
+        const int m0 = tc.m_tile * kBlockM;
+        int b0_row, b1_row;
+        if (kMode == kGatedSplit) {
+          b0_row = tc.n_tile * 128;  // rows of W_gate
+          b1_row = tc.n_tile * 128;  // rows of W_up
+        } else {
+          b0_row = tc.n_tile * 256;
+          b1_row = b0_row + 128;
+        }
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!wd.wait(empty_bar(stage), phase ^ 1u, kSiteProducerEmpty)) {
+            alive = false;
+            break;
+          }
+          const uint32_t a_dst = smem_base + stage * kStageBytes;
+          const uint32_t b_dst = a_dst + kATileBytes;
+          mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
+          tma_load_2d(a_dst, &map_a, full_bar(stage), kb * kBlockK, m0);
+          tma_load_2d(b_dst, &map_b0, full_bar(stage), kb * kBlockK, b0_row);
+          tma_load_2d(b_dst + kBHalfBytes, &map_b1, full_bar(stage), kb * kBlockK, b1_row);
+          issued_mask |= 1u << stage;
+          last_parity_mask = (last_parity_mask & ~(1u << stage)) | (phase << stage);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (wd.aborted()) {
+        // Unwinding: let every copy this thread started land before the CTA exits.
+        for (int s = 0; s < kStages; ++s) {
+          if (issued_mask & (1u << s)) {
+            const uint32_t par = (last_parity_mask >> s) & 1u;
+            const unsigned long long t0 = global_timer_ns();
+            while (!mbar_try_wait(full_bar(s), par)) {
+              if (global_timer_ns() - t0 > 50000000ull) {  // 50 ms
+                wd.give_up(kSiteDrainTma);
+                break;
+              }
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16_f32(kBlockM, kUmmaN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+        if (!wd.wait(tempty_bar(acc), acc_phase ^ 1u, kSiteMmaTmemEmpty)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kUmmaN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!wd.wait(full_bar(stage), phase, kSiteMmaFull)) {
+            alive = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_base + stage * kStageBytes;
+          const uint64_t a_desc = umma_desc_k_sw128(a_addr);
+          const uint64_t b_desc = umma_desc_k_sw128(a_addr + kATileBytes);
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            // advance 16 elements = 32 bytes along K inside the swizzled row: +2 in >>4 units
+            umma_bf16_ss(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc,
+                         (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));  // stage reusable once these MMAs retire
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!alive) break;
+        umma_commit(tfull_bar(acc));  // accumulator complete
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+      if (wd.aborted()) {
+        // Unwinding: wait for whatever MMAs are still in flight before TMEM is freed.
+        umma_commit(drain_bar);
+        const unsigned long long t0 = global_timer_ns();
+        while (!mbar_try_wait(drain_bar, 0)) {
+          if (global_timer_ns() - t0 > 50000000ull) {
+            wd.give_up(kSiteDrainMma);
+            break;
+          }
+        }
+      }
+    }
+  } else {
+    // -------------------------------- epilogue --------------------------------
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+    const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      const TileCoord tc = tile_coord(tile, p);
+      uint32_t ok = 1;
+      if (lane == 0) ok = wd.wait(tfull_bar(acc), acc_phase, kSiteEpilogueFull) ? 1u : 0u;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      __syncwarp();
+      tc_fence_after_sync();
+      const uint32_t t_acc = tmem_base + lane_field + static_cast<uint32_t>(acc * kUmmaN);
+      const int row = tc.m_tile * kBlockM + quarter * 32 + static_cast<int>(lane);
+
+      if constexpr (kMode == kPlain) {
+        const int col_base = tc.n_tile * 256;
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {
+          if (col_base + c * 32 >= p.n_out) break;  // warp-uniform
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_acc + c * 32, r);
+          tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          store_chunk32<kOutF32>(p, row, col_base + c * 32, v);
+        }
+      } else if constexpr (kMode == kGatedSplit) {
+        const int col_base = tc.n_tile * 128;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          if (col_base + c * 32 >= p.n_out) break;
+          uint32_t g[32], u[32];
+          tmem_ld_32x32b_x32(t_acc + c * 32, g);        // gate columns [0,128)
+          tmem_ld_32x32b_x32(t_acc + 128 + c * 32, u);  // up columns [128,256)
+          tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = silu_mul(__uint_as_float(g[i]), __uint_as_float(u[i]));
+          store_chunk32<false>(p, row, col_base + c * 32, v);
+        }
+      } else {
+        const int col_base = tc.n_tile * 128;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          if (col_base + c * 32 >= p.n_out) break;
+          uint32_t lo[32], hi[32];
+          tmem_ld_32x32b_x32(t_acc + c * 64, lo);
+          tmem_ld_32x32b_x32(t_acc + c * 64 + 32, hi);
+          tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            // accumulator column 2j = up (linear), 2j+1 = gate (SiLU)
+            v[i] = silu_mul(__uint_as_float(lo[2 * i + 1]), __uint_as_float(lo[2 * i]));
+            v[16 + i] = silu_mul(__uint_as_float(hi[2 * i + 1]), __uint_as_float(hi[2 * i]));
+          }
+          store_chunk32<false>(p, row, col_base + c * 32, v);
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(tempty_bar(acc));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  // -------------------------------- teardown ----------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace fsw

@@ -1,0 +1,145 @@
+// Operator boundary: the same Python module (`fused_mlp_module`) and dispatcher library
+// (`ASMLLM`) as the reference's csrc/torch_bindings.cpp:27-50, with the same two ops
+//
+//   fused_swiglu_bf16(Tensor X, Tensor W1W3) -> Tensor
+//   swiglu_fwd_bf16(int m, int n, int k, Tensor A, int ldA, Tensor B, int ldB, Tensor C, int ldC) -> ()
+//
+// plus the split-weight and whole-MLP ops the reference lacks.  This file is the only one
+// that sees torch types: it validates tensors, takes the current device / stream and hands
+// raw pointers to the C ABI in include/fswiglu.h.  A non-zero status becomes a c10::Error
+// (RuntimeError in Python), like the reference's TORCH_CHECKs (csrc/SwiGLU/swiglu.cu:475-480).
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "fswiglu.h"
+
+namespace {
+
+void check_status(int rc, const char* where) {
+  TORCH_CHECK(rc == FSWIGLU_OK, where, ": ", fswiglu_status_string(rc), " (status ", rc, ")");
+}
+
+void check_bf16_cuda(const at::Tensor& t, const char* name) {
+  TORCH_CHECK(t.scalar_type() == at::kBFloat16, name, " must be a bfloat16 tensor");
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+}
+
+int64_t row_pitch(const at::Tensor& t, const char* name) {
+  TORCH_CHECK(t.dim() == 2, name, " must be 2-D");
+  TORCH_CHECK(t.size(1) <= 1 || t.stride(1) == 1, name, " must have unit stride along its last dimension");
+  return t.size(0) > 1 ? t.stride(0) : std::max<int64_t>(t.stride(0), t.size(1));
+}
+
+void* current_stream(const at::Tensor& t) {
+  return static_cast<void*>(at::cuda::getCurrentCUDAStream(t.get_device()).stream());
+}
+
+}  // namespace
+
+// Raw launcher, reference semantics (csrc/SwiGLU/swiglu.cu:397-525): leading dimensions in elements,
+// B holds up rows at even and gate rows at odd indices, the [m, n/2] result is written into C with
+// row stride ldC/2.
+void swiglu_fwd_bf16(int64_t m, int64_t n, int64_t k, at::Tensor const& A, int64_t ldA, at::Tensor const& B,
+                     int64_t ldB, at::Tensor const& C, int64_t ldC) {
+  check_bf16_cuda(A, "A");
+  check_bf16_cuda(B, "B");
+  check_bf16_cuda(C, "C");
+  TORCH_CHECK(n % 2 == 0 && ldC % 2 == 0, "n and ldC must be even (up/gate rows are interleaved)");
+  const c10::cuda::OptionalCUDAGuard guard(device_of(A));
+  check_status(fswiglu_gateup_bf16(A.data_ptr(), ldA, B.data_ptr(), ldB, nullptr, C.data_ptr(), ldC / 2, m, n / 2,
+                                   k, 1, current_stream(A)),
+               "swiglu_fwd_bf16");
+}
+
+// Convenience wrapper, reference semantics (csrc/SwiGLU/swiglu.cu:538-553): allocates [M, N/2].
+at::Tensor fused_swiglu_bf16(at::Tensor const& X, at::Tensor const& W1W3) {
+  check_bf16_cuda(X, "X");
+  check_bf16_cuda(W1W3, "W1W3");
+  const int64_t M = X.size(0), N = W1W3.size(0), K = X.size(1);
+  at::Tensor out = at::empty({M, N / 2}, X.options());
+  swiglu_fwd_bf16(M, N, K, X, row_pitch(X, "X"), W1W3, row_pitch(W1W3, "W1W3"), out, N);
+  return out;
+}
+
+at::Tensor fused_swiglu_gateup_bf16(at::Tensor const& x, at::Tensor const& W_gate, at::Tensor const& W_up) {
+  check_bf16_cuda(x, "x");
+  check_bf16_cuda(W_gate, "W_gate");
+  check_bf16_cuda(W_up, "W_up");
+  const int64_t M = x.size(0), d = x.size(1), F = W_gate.size(0);
+  TORCH_CHECK(W_up.sizes() == W_gate.sizes() && W_gate.size(1) == d, "W_gate and W_up must both be [F, d]");
+  const int64_t ldw = row_pitch(W_gate, "W_gate");
+  TORCH_CHECK(row_pitch(W_up, "W_up") == ldw, "W_gate and W_up must share one leading dimension");
+  at::Tensor h = at::empty({M, F}, x.options());
+  const c10::cuda::OptionalCUDAGuard guard(device_of(x));
+  check_status(fswiglu_gateup_bf16(x.data_ptr(), row_pitch(x, "x"), W_gate.data_ptr(), ldw, W_up.data_ptr(),
+                                   h.data_ptr(), F, M, F, d, 0, current_stream(x)),
+               "fused_swiglu_gateup_bf16");
+  return h;
+}
+
+at::Tensor swiglu_down_bf16(at::Tensor const& h, at::Tensor const& W_down, bool fp32_out) {
+  check_bf16_cuda(h, "h");
+  check_bf16_cuda(W_down, "W_down");
+  const int64_t M = h.size(0), F = h.size(1), d = W_down.size(0);
+  TORCH_CHECK(W_down.size(1) == F, "W_down must be [d, F]");
+  at::Tensor out = at::empty({M, d}, h.options().dtype(fp32_out ? at::kFloat : at::kBFloat16));
+  const c10::cuda::OptionalCUDAGuard guard(device_of(h));
+  check_status(fswiglu_down_bf16(h.data_ptr(), row_pitch(h, "h"), W_down.data_ptr(), row_pitch(W_down, "W_down"),
+                                 out.data_ptr(), d, M, d, F, fp32_out ? FSWIGLU_OUT_F32 : FSWIGLU_OUT_BF16,
+                                 current_stream(h)),
+               "swiglu_down_bf16");
+  return out;
+}
+
+at::Tensor fused_swiglu_mlp_bf16(at::Tensor const& x, at::Tensor const& W_gate, at::Tensor const& W_up,
+                                 at::Tensor const& W_down) {
+  check_bf16_cuda(x, "x");
+  check_bf16_cuda(W_gate, "W_gate");
+  check_bf16_cuda(W_up, "W_up");
+  check_bf16_cuda(W_down, "W_down");
+  const int64_t M = x.size(0), d = x.size(1), F = W_gate.size(0);
+  TORCH_CHECK(W_up.sizes() == W_gate.sizes() && W_gate.size(1) == d && W_down.size(0) == d && W_down.size(1) == F,
+              "expected W_gate/W_up [F, d] and W_down [d, F]");
+  const int64_t ldw = row_pitch(W_gate, "W_gate");
+  TORCH_CHECK(row_pitch(W_up, "W_up") == ldw, "W_gate and W_up must share one leading dimension");
+  at::Tensor out = at::empty({M, d}, x.options());
+  if (M == 0) return out;
+  const int64_t ws_bytes = static_cast<int64_t>(fswiglu_workspace_bytes(M, d, F));
+  at::Tensor ws = at::empty({std::max<int64_t>(ws_bytes, 256)}, x.options().dtype(at::kByte));
+  const c10::cuda::OptionalCUDAGuard guard(device_of(x));
+  check_status(fswiglu_mlp_bf16(x.data_ptr(), row_pitch(x, "x"), W_gate.data_ptr(), W_up.data_ptr(), ldw,
+                                W_down.data_ptr(), row_pitch(W_down, "W_down"), out.data_ptr(), d, FSWIGLU_OUT_BF16,
+                                M, d, F, ws.data_ptr(), static_cast<size_t>(ws.numel()), current_stream(x)),
+               "fused_swiglu_mlp_bf16");
+  return out;
+}
+
+namespace Fused_MLP {
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("fused_swiglu_bf16", &fused_swiglu_bf16, "fused SwiGLU for bf16");
+  m.def("swiglu_fwd_bf16", &swiglu_fwd_bf16, "SwiGLU fwd bf16");
+  m.def("fused_swiglu_gateup_bf16", &fused_swiglu_gateup_bf16, "silu(x Wg^T) * (x Wu^T), split weights");
+  m.def("swiglu_down_bf16", &swiglu_down_bf16, "h Wd^T", pybind11::arg("h"), pybind11::arg("W_down"),
+        pybind11::arg("fp32_out") = false);
+  m.def("fused_swiglu_mlp_bf16", &fused_swiglu_mlp_bf16, "(silu(x Wg^T) * (x Wu^T)) Wd^T");
+}
+
+TORCH_LIBRARY(ASMLLM, m) {
+  m.def("fused_swiglu_bf16(Tensor X, Tensor W1W3) -> Tensor");
+  m.def("swiglu_fwd_bf16(int m, int n, int k, Tensor A, int ldA, Tensor B, int ldB, Tensor C, int ldC) -> ()");
+  m.def("fused_swiglu_gateup_bf16(Tensor x, Tensor W_gate, Tensor W_up) -> Tensor");
+  m.def("swiglu_down_bf16(Tensor h, Tensor W_down, bool fp32_out=False) -> Tensor");
+  m.def("fused_swiglu_mlp_bf16(Tensor x, Tensor W_gate, Tensor W_up, Tensor W_down) -> Tensor");
+}
+
+TORCH_LIBRARY_IMPL(ASMLLM, CUDA, m) {
+  m.impl("fused_swiglu_bf16", &fused_swiglu_bf16);
+  m.impl("swiglu_fwd_bf16", &swiglu_fwd_bf16);
+  m.impl("fused_swiglu_gateup_bf16", &fused_swiglu_gateup_bf16);
+  m.impl("swiglu_down_bf16", &swiglu_down_bf16);
+  m.impl("fused_swiglu_mlp_bf16", &fused_swiglu_mlp_bf16);
+}
+
+}  // namespace Fused_MLP

@@ -1,0 +1,92 @@
+"""ctypes binding of libfswiglu.so (the C ABI declared in include/fswiglu.h).
+
+Every compute entry point of this package goes through the functions below; there
+is no PyTorch or CPU fallback.  If the shared library has not been built, importing
+this module raises, so a missing CUDA build can never pass silently.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libfswiglu.so")
+
+OK = 0
+ERR_BAD_ARG = -1
+ERR_ALIGNMENT = -2
+ERR_SHAPE = -3
+ERR_CUDA = -4
+ERR_WATCHDOG = -5
+ERR_WORKSPACE = -6
+ERR_NO_DEVICE = -7
+
+OUT_BF16 = 0
+OUT_F32 = 1
+
+# name -> (restype, argtypes); mirrors include/fswiglu.h one to one.
+_vp, _i64, _int, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t
+SIGNATURES = {
+    "fswiglu_gateup_bf16": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp]),
+    "fswiglu_down_bf16": (_int, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _int, _vp]),
+    "fswiglu_mlp_bf16": (_int, [_vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _int, _i64, _i64, _i64,
+                                _vp, _sz, _vp]),
+    "fswiglu_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "fswiglu_mlp_bf16_host": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _sz, _vp]),
+    "fswiglu_host_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "fswiglu_device_status": (_int, [ctypes.POINTER(ctypes.c_uint32), _vp]),
+    "fswiglu_status_string": (ctypes.c_char_p, [_int]),
+    "fswiglu_version": (ctypes.c_char_p, []),
+    "fswiglu_launch_count": (ctypes.c_uint64, []),
+}
+
+
+class FswigluError(RuntimeError):
+    """A libfswiglu call returned a negative status."""
+
+    def __init__(self, status: int, where: str):
+        self.status = status
+        super().__init__(f"{where}: {status_string(status)} (status {status})")
+
+
+def _load() -> ctypes.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it first (python -c 'import __graft_entry__ as g; g.build()' "
+            "or python fused-swiglu_b200/build.py). There is no fallback path."
+        )
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (restype, argtypes) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError here = header and library disagree
+        fn.restype = restype
+        fn.argtypes = argtypes
+    return lib
+
+
+lib = _load()
+
+
+def status_string(status: int) -> str:
+    return lib.fswiglu_status_string(int(status)).decode()
+
+
+def version() -> str:
+    return lib.fswiglu_version().decode()
+
+
+def launch_count() -> int:
+    return int(lib.fswiglu_launch_count())
+
+
+def check(status: int, where: str) -> None:
+    if status != OK:
+        raise FswigluError(status, where)
+
+
+def device_status(stream_ptr: int = 0) -> int:
+    """Synchronise the stream and return the device watchdog word (0 = healthy)."""
+    word = ctypes.c_uint32(0)
+    rc = lib.fswiglu_device_status(ctypes.byref(word), ctypes.c_void_p(stream_ptr))
+    if rc not in (OK, ERR_WATCHDOG):
+        raise FswigluError(rc, "fswiglu_device_status")
+    return int(word.value)

@@ -1,0 +1,121 @@
+/*
+ * fswiglu.h -- C ABI of the B200 (sm_100a) fused SwiGLU MLP forward library, libfswiglu.so.
+ *
+ * The reference project (bit-ml/Fused-SwiGLU) has no C ABI: torch tensors cross its
+ * operator boundary directly (csrc/torch_bindings.cpp:27-50).  This header is the
+ * torch-free boundary underneath that operator surface; the torch extension
+ * `fused_mlp_module` (same module and op names as the reference) is a thin caller of
+ * these entry points, and so is any other host (ctypes, cgo, JNI ...).
+ *
+ * Conventions
+ *   - all matrices are row-major bf16 in device memory of the CURRENT device; leading
+ *     dimensions (ld*) are in ELEMENTS;
+ *   - x [M, d], W_gate / W_up [F, d], h [M, F], W_down [d, F], out [M, d];
+ *   - every call is asynchronous on `stream` (a cudaStream_t passed as void*), never
+ *     synchronises, never throws; it returns FSWIGLU_OK or a negative status;
+ *   - requirements checked on entry: 16-byte aligned base pointers, d % 8 == 0 and
+ *     F % 8 == 0 (TMA needs 16-byte row pitches), ld >= row length, ld % 8 == 0 for
+ *     TMA-read operands; M, d, F may otherwise be ragged (not tile multiples);
+ *   - M == 0 (empty batch) is a successful no-op;
+ *   - there is no CPU fallback: without a usable sm_100 device the calls fail.
+ */
+#ifndef FSWIGLU_H_
+#define FSWIGLU_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  FSWIGLU_OK = 0,
+  FSWIGLU_ERR_BAD_ARG = -1,    /* null pointer, negative size, unknown enum value      */
+  FSWIGLU_ERR_ALIGNMENT = -2,  /* base pointer or leading dimension not 16-byte aligned */
+  FSWIGLU_ERR_SHAPE = -3,      /* d or F not a multiple of 8, ld too small, size > 2^31 */
+  FSWIGLU_ERR_CUDA = -4,       /* CUDA runtime / driver call or kernel launch failed    */
+  FSWIGLU_ERR_WATCHDOG = -5,   /* a bounded device-side wait gave up (see device_status)*/
+  FSWIGLU_ERR_WORKSPACE = -6,  /* workspace missing or smaller than workspace_bytes()   */
+  FSWIGLU_ERR_NO_DEVICE = -7   /* current device is not compute capability 10.x         */
+};
+
+/* Output element type of the down projection. */
+enum { FSWIGLU_OUT_BF16 = 0, FSWIGLU_OUT_F32 = 1 };
+
+/*
+ * Gate-up projection fused with the SwiGLU gate:  h = silu(x Wg^T) * (x Wu^T).
+ *
+ * Replaces the reference's swiglu_fwd<bf16,bf16,bf16> host launcher and its kernel
+ * (csrc/SwiGLU/swiglu.cu:397-525 and :103-394; bound as `swiglu_fwd_bf16` at
+ * csrc/torch_bindings.cpp:35,42,49).
+ *
+ *   interleaved == 0 : w_gate_or_w13 = W_gate [F, d], w_up = W_up [F, d]
+ *   interleaved != 0 : w_gate_or_w13 = the reference's packed W1W3 [2F, d] with row 2j = up_j and
+ *                      row 2j+1 = gate_j (csrc/SwiGLU/swiglu.cu:376-383); w_up must be NULL.
+ *                      With ldh = ldC / 2 this is bit-for-bit the reference call
+ *                      swiglu_fwd_bf16(M, 2F, d, x, ldx, W1W3, ldw, C, ldC).
+ */
+int fswiglu_gateup_bf16(const void* x, int64_t ldx, const void* w_gate_or_w13, int64_t ldw,
+                        const void* w_up, void* h, int64_t ldh, int64_t M, int64_t F, int64_t d,
+                        int interleaved, void* stream);
+
+/*
+ * Down projection  out = h Wd^T  (absent from the reference, whose kernel stops at h; required by
+ * the full-MLP expression (silu(x Wg^T) * (x Wu^T)) Wd^T the build is checked against).
+ * out_dtype: FSWIGLU_OUT_BF16 (one rounding of the fp32 accumulator) or FSWIGLU_OUT_F32 (tensor-
+ * parallel partial sums that are reduced before rounding).
+ */
+int fswiglu_down_bf16(const void* h, int64_t ldh, const void* w_down, int64_t ldw, void* out,
+                      int64_t ldo, int64_t M, int64_t d, int64_t F, int out_dtype, void* stream);
+
+/*
+ * Whole MLP forward on device buffers:  out = (silu(x Wg^T) * (x Wu^T)) Wd^T.
+ * `workspace` holds the bf16 hidden activations (and, for M <= 64, the split-K partial sums of the
+ * decode path); it must be 256-byte aligned and at least fswiglu_workspace_bytes(M, d, F) long.
+ * The eager expression it replaces: numeric_tests.py:41-43 (gate-up part) extended with the down
+ * projection.
+ */
+int fswiglu_mlp_bf16(const void* x, int64_t ldx, const void* w_gate, const void* w_up, int64_t ldw_gu,
+                     const void* w_down, int64_t ldw_d, void* out, int64_t ldo, int out_dtype,
+                     int64_t M, int64_t d, int64_t F, void* workspace, size_t workspace_bytes,
+                     void* stream);
+
+/* Bytes of workspace fswiglu_mlp_bf16 needs for this problem size (0 when M == 0). */
+size_t fswiglu_workspace_bytes(int64_t M, int64_t d, int64_t F);
+
+/*
+ * Same MLP forward with HOST buffers for the activations: x_host [M, d] and out_host [M, d] are
+ * (ideally pinned) host memory, weights stay resident on the device.  Rows are independent, so the
+ * call cuts M into slabs and overlaps host->device copy, compute and device->host copy of
+ * successive slabs on three internal streams ordered after `stream`; it returns after the last
+ * slab has landed in out_host (this call synchronises).  Device staging comes from `workspace`
+ * (fswiglu_host_workspace_bytes).
+ */
+int fswiglu_mlp_bf16_host(const void* x_host, const void* w_gate, const void* w_up,
+                          const void* w_down, void* out_host, int64_t M, int64_t d, int64_t F,
+                          void* workspace, size_t workspace_bytes, void* stream);
+size_t fswiglu_host_workspace_bytes(int64_t M, int64_t d, int64_t F);
+
+/*
+ * Device-side watchdog.  Kernels never spin forever: a wait that exceeds its limit records where it
+ * gave up and the kernel unwinds.  This call synchronises `stream`, copies the status word of the
+ * current device into *status (0 = healthy), clears it, and returns FSWIGLU_ERR_WATCHDOG if it
+ * was non-zero.
+ */
+int fswiglu_device_status(uint32_t* status, void* stream);
+
+/* Human-readable name of a status code returned by this library. */
+const char* fswiglu_status_string(int status);
+
+/* Library version, "major.minor.patch". */
+const char* fswiglu_version(void);
+
+/* Number of kernels this library has launched in this process (for launch accounting). */
+uint64_t fswiglu_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* FSWIGLU_H_ */
