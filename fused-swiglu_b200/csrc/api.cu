@@ -14,6 +14,31 @@
 #include "decode_sm100.cuh"
 #include "gemm_sm100.cuh"
 
+namespace fsw {
+
+// fp32 -> bf16 (RNE), 8 elements per thread per step, grid-stride.
+__global__ void __launch_bounds__(256) cast_f32_to_bf16_kernel(const float4* __restrict__ src,
+                                                                uint4* __restrict__ dst, long long n8,
+                                                                const float* __restrict__ src_tail,
+                                                                __nv_bfloat16* __restrict__ dst_tail, int tail) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += stride) {
+    const float4 a = src[2 * i];
+    const float4 b = src[2 * i + 1];
+    uint4 q;
+    q.x = pack_bf16x2(a.x, a.y);
+    q.y = pack_bf16x2(a.z, a.w);
+    q.z = pack_bf16x2(b.x, b.y);
+    q.w = pack_bf16x2(b.z, b.w);
+    dst[i] = q;
+  }
+  if (blockIdx.x == 0 && static_cast<int>(threadIdx.x) < tail) {
+    dst_tail[threadIdx.x] = __float2bfloat16_rn(src_tail[threadIdx.x]);
+  }
+}
+
+}  // namespace fsw
+
 namespace {
 
 using namespace fsw;
@@ -358,6 +383,25 @@ int fswiglu_mlp_bf16_host(const void* x_host, const void* w_gate, const void* w_
                        cudaStreamSynchronize(st->d2h_stream) == cudaSuccess;
   if (rc != FSWIGLU_OK) return rc;
   return (ok && drained) ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
+}
+
+int fswiglu_cast_f32_to_bf16(const void* src, void* dst, int64_t n, void* stream) {
+  if (n < 0 || (n > 0 && (src == nullptr || dst == nullptr))) return FSWIGLU_ERR_BAD_ARG;
+  if (n == 0) return FSWIGLU_OK;
+  if (!aligned16(src) || !aligned16(dst)) return FSWIGLU_ERR_ALIGNMENT;
+  DeviceState* st = nullptr;
+  if (int rc = device_state(&st)) return rc;
+  const long long n8 = n / 8;
+  const int tail = static_cast<int>(n - n8 * 8);
+  long long blocks = (n8 + 255) / 256;
+  const long long cap = static_cast<long long>(st->num_sms) * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  cast_f32_to_bf16_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float4*>(src), static_cast<uint4*>(dst), n8, static_cast<const float*>(src) + n8 * 8,
+      static_cast<__nv_bfloat16*>(dst) + n8 * 8, tail);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
 }
 
 int fswiglu_device_status(uint32_t* status, void* stream) {

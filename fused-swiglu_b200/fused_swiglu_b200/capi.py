@@ -34,6 +34,7 @@ SIGNATURES = {
     "fswiglu_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "fswiglu_mlp_bf16_host": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _sz, _vp]),
     "fswiglu_host_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "fswiglu_cast_f32_to_bf16": (_int, [_vp, _vp, _i64, _vp]),
     "fswiglu_device_status": (_int, [ctypes.POINTER(ctypes.c_uint32), _vp]),
     "fswiglu_status_string": (ctypes.c_char_p, [_int]),
     "fswiglu_version": (ctypes.c_char_p, []),

@@ -98,6 +98,13 @@ int fswiglu_mlp_bf16_host(const void* x_host, const void* w_gate, const void* w_
 size_t fswiglu_host_workspace_bytes(int64_t M, int64_t d, int64_t F);
 
 /*
+ * dst[i] = bf16(src[i]) for n contiguous elements (round to nearest even): the single rounding after
+ * tensor-parallel fp32 partial sums have been reduced.  No counterpart in the reference (single GPU).
+ * src and dst must be 16-byte aligned.
+ */
+int fswiglu_cast_f32_to_bf16(const void* src, void* dst, int64_t n, void* stream);
+
+/*
  * Device-side watchdog.  Kernels never spin forever: a wait that exceeds its limit records where it
  * gave up and the kernel unwinds.  This call synchronises `stream`, copies the status word of the
  * current device into *status (0 = healthy), clears it, and returns FSWIGLU_ERR_WATCHDOG if it

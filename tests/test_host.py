@@ -1,0 +1,130 @@
+"""Host-side logic that needs no GPU: weight layouts, shard bounds, seeded inputs, and that
+the C-ABI library loads and exports every symbol include/fswiglu.h declares."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+from fused_swiglu_b200 import capi, inputs, pack
+from fused_swiglu_b200.tp import TensorParallelSwiGLU
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "fswiglu.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(fswiglu_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    names = declared_symbols()
+    assert len(names) >= 10
+    raw = ctypes.CDLL(capi.LIB_PATH)
+    for n in names:
+        assert hasattr(raw, n), f"{n} declared in include/fswiglu.h but not exported"
+    assert sorted(capi.SIGNATURES) == names, "ctypes signature table and header disagree"
+
+
+def test_status_strings_and_version():
+    assert capi.status_string(capi.OK) == "ok"
+    for code in range(-7, 0):
+        assert capi.status_string(code) != "unknown status"
+    assert capi.status_string(-99) == "unknown status"
+    assert re.fullmatch(r"\d+\.\d+\.\d+", capi.version())
+
+
+def test_workspace_sizes_are_host_arithmetic():
+    assert capi.lib.fswiglu_workspace_bytes(0, 4096, 11008) == 0
+    assert capi.lib.fswiglu_workspace_bytes(4096, 4096, 11008) >= 4096 * 11008 * 2
+    assert capi.lib.fswiglu_host_workspace_bytes(4096, 4096, 11008) >= 2 * 4096 * 4096 * 2
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-GPU failure mode")
+def test_compute_calls_fail_loudly_without_a_gpu():
+    """No CPU fallback: on a machine without an sm_100 device the entry points return an error."""
+    buf = (ctypes.c_uint16 * 64)()
+    p = ctypes.cast(buf, ctypes.c_void_p)
+    rc = capi.lib.fswiglu_gateup_bf16(p, 8, p, 8, p, p, 8, 1, 8, 8, 0, None)
+    assert rc == capi.ERR_NO_DEVICE
+    with pytest.raises(capi.FswigluError):
+        capi.check(rc, "fswiglu_gateup_bf16")
+
+
+def test_ops_reject_cpu_and_wrong_dtype_tensors():
+    from fused_swiglu_b200 import ops
+
+    a = torch.zeros((4, 8), dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        ops.fused_swiglu_bf16(a, torch.zeros((8, 8), dtype=torch.bfloat16))
+    with pytest.raises(RuntimeError, match="bfloat16"):
+        ops.fused_swiglu_bf16(a.float(), torch.zeros((8, 8)))
+
+
+def test_interleave_roundtrip():
+    g = torch.Generator().manual_seed(0)
+    up = torch.randn((10, 16), generator=g).to(torch.bfloat16)
+    gate = torch.randn((10, 16), generator=g).to(torch.bfloat16)
+    w13 = pack.interleave_up_gate(up, gate)
+    assert w13.shape == (20, 16)
+    assert torch.equal(w13[0::2], up) and torch.equal(w13[1::2], gate)
+    u2, g2 = pack.split_up_gate(w13)
+    assert torch.equal(u2, up) and torch.equal(g2, gate)
+    with pytest.raises(ValueError):
+        pack.split_up_gate(w13[:19])
+
+
+@pytest.mark.parametrize("F,world", [(28672, 8), (13824, 8), (11008, 4), (200, 3), (8, 8), (14336, 1)])
+def test_shard_bounds_partition(F, world):
+    spans = [pack.shard_bounds(F, world, r) for r in range(world)]
+    assert spans[0][0] == 0 and spans[-1][1] == F
+    for (lo, hi), (lo2, _) in zip(spans, spans[1:]):
+        assert hi == lo2 and lo <= hi
+    for lo, hi in spans[:-1]:
+        assert (hi - lo) % 8 == 0
+    assert pack.shard_bounds(13824, 8, 0) == (0, 1728)
+
+
+def test_shard_weights_shapes():
+    wg = torch.arange(24 * 16, dtype=torch.float32).reshape(24, 16)
+    wd = torch.arange(16 * 24, dtype=torch.float32).reshape(16, 24)
+    g, u, dn = pack.shard_mlp_weights(wg, wg + 1, wd, 3, 1)
+    assert g.shape == (8, 16) and dn.shape == (16, 8) and dn.is_contiguous()
+    assert torch.equal(g, wg[8:16]) and torch.equal(dn, wd[:, 8:16])
+
+
+def test_seeded_inputs_are_deterministic_and_shaped():
+    a = inputs.make_mlp_inputs(8, 16, 24, seed=0)
+    b = inputs.make_mlp_inputs(8, 16, 24, seed=0)
+    for s, t in zip(a, b):
+        assert torch.equal(s, t) and s.dtype == torch.bfloat16
+    assert a[0].shape == (8, 16) and a[1].shape == (24, 16) and a[3].shape == (16, 24)
+    assert float(a[1].float().std()) == pytest.approx(0.02, rel=0.2)
+    c = inputs.make_mlp_inputs(8, 16, 24, seed=1)
+    assert not torch.equal(a[0], c[0])
+
+
+def test_ragged_batch_length_matches_survey_value():
+    assert int(inputs.ragged_lengths(0).sum()) == 32414
+    assert 32414 % 128 == 30
+
+
+def test_outliers_present():
+    g = torch.Generator().manual_seed(0)
+    x = inputs.make_x(256, 256, g, outliers=True).float()
+    frac = float((x.abs() > 6).float().mean())
+    assert 0.003 < frac < 0.02
+
+
+def test_tp_slab_bounds_cover_rows():
+    w = torch.zeros((8, 16))
+    for mode in ("allreduce", "rs_ag"):
+        tp = TensorParallelSwiGLU(w, w, torch.zeros((16, 8)), n_slabs=4, mode=mode,
+                                  local_partial=lambda *a: None, round_fn=lambda s, d: None)
+        for M in (1, 7, 100, 4096, 32414):
+            b = tp.slab_bounds(M)
+            assert b[0][0] == 0 and b[-1][1] == M
+            assert all(x[1] == y[0] for x, y in zip(b, b[1:]))
+            assert len(b) <= 4

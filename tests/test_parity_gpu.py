@@ -1,0 +1,322 @@
+"""GPU parity tests: every compute call goes through the C ABI (ctypes) and is compared with
+the CPU oracle on the same seeded inputs, with the committed golden fixtures, and - at the
+full benchmark sizes - through row-subset oracles and size-independent properties.
+
+Tolerances (bf16 tensors, fp32 accumulation), written out per test:
+  * against the oracle with the SAME rounding points (fp32 acc, fp32 gate, one bf16 rounding):
+    at most one bf16 ulp on entries where the fp32 value sits next to a rounding boundary;
+    gated on rel-Fro <= 1e-3 and scaled max-abs <= 2^-7;
+  * against the fp32 expression (silu(x Wg^T) * (x Wu^T)) Wd^T: rel-Fro <= 5e-3 everywhere;
+    raw max-abs <= 2e-2 where |out| stays below 8 (configuration 1), scaled max-abs
+    (max-abs / max|ref|) <= 8e-3 elsewhere, because half a bf16 ulp of the largest outputs
+    already exceeds 2e-2 there.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import swiglu_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+REL_FRO_SAME_ROUNDING = 1e-3
+REL_FRO_GRADED = 5e-3
+MAX_ABS_GRADED = 2e-2
+SCALED_MAX_ABS = 8e-3
+
+
+def f32(t):
+    return t.detach().float().cpu().numpy()
+
+
+def bf16_from_bits(a, dev):
+    return torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16).to(dev)
+
+
+@pytest.fixture(scope="module")
+def fsw(cuda_dev):
+    import fused_swiglu_b200 as pkg
+
+    yield pkg
+    torch.cuda.synchronize()
+    assert pkg.capi.device_status() == 0, "device watchdog tripped during the module"
+
+
+def healthy(fsw):
+    torch.cuda.synchronize()
+    assert fsw.capi.device_status() == 0
+
+
+# ------------------------------------------------------------------ golden fixtures
+@pytest.mark.parametrize("name", ["gateup_interleaved_small.npz", "gateup_interleaved_unit.npz"])
+def test_packed_op_against_golden(fsw, cuda_dev, golden_dir, name):
+    z = np.load(os.path.join(golden_dir, name))
+    A, B = bf16_from_bits(z["A"], cuda_dev), bf16_from_bits(z["B"], cuda_dev)
+    out = fsw.ops.fused_swiglu_bf16(A, B)
+    healthy(fsw)
+    assert out.shape == (A.size(0), B.size(0) // 2) and out.dtype == torch.bfloat16
+    m = orc.error_metrics(f32(out), z["out_fp32"])
+    # fp32 reference lines vs one bf16 rounding of the result: half an ulp, 2^-9 relative
+    assert m["rel_fro"] <= 3e-3, m
+    # and the reference's own bf16-eager oracle differs from us by its extra roundings only
+    m2 = orc.error_metrics(f32(out), orc.bf16_bits_to_f32(z["out_eager_bf16"]))
+    assert m2["rel_fro"] <= REL_FRO_GRADED, m2
+    # same rounding points -> (almost) bit-exact
+    same = orc.gateup_interleaved_fp32acc(orc.bf16_bits_to_f32(z["A"]), orc.bf16_bits_to_f32(z["B"]))
+    m3 = orc.error_metrics(f32(out), same)
+    assert m3["rel_fro"] <= REL_FRO_SAME_ROUNDING and m3["scaled_max_abs"] <= 2.0 ** -7, m3
+    assert (f32(out) != same).mean() < 0.02
+
+
+@pytest.mark.parametrize("name", ["mlp_small.npz", "mlp_ragged_outliers.npz"])
+def test_mlp_against_golden(fsw, cuda_dev, golden_dir, name):
+    z = np.load(os.path.join(golden_dir, name))
+    x, wg, wu, wd = (bf16_from_bits(z[k], cuda_dev) for k in ("x", "w_gate", "w_up", "w_down"))
+    out = fsw.ops.fused_swiglu_mlp_bf16(x, wg, wu, wd)
+    healthy(fsw)
+    m = orc.error_metrics(f32(out), z["out_fp32"])
+    assert m["rel_fro"] <= REL_FRO_GRADED and m["scaled_max_abs"] <= SCALED_MAX_ABS, m
+
+
+# ------------------------------------------------------------------ oracle, same rounding points
+SHAPES = [
+    (1, 64, 8), (1, 8, 8), (5, 72, 40), (127, 64, 128), (128, 64, 128), (129, 192, 136), (200, 520, 264),
+    (256, 4096, 256), (300, 1000, 520), (1024, 512, 1152),
+]
+
+
+@pytest.mark.parametrize("M,d,F", SHAPES)
+def test_gateup_split_matches_oracle(fsw, cuda_dev, M, d, F):
+    x, wg, wu, _ = fsw.inputs.make_mlp_inputs(M, d, F, seed=M + d + F)
+    wg, wu = wg * 25, wu * 25  # unit-scale pre-activations so that SiLU is exercised off its linear part
+    h = fsw.ops.fused_swiglu_gateup_bf16(x.to(cuda_dev), wg.to(cuda_dev), wu.to(cuda_dev))
+    healthy(fsw)
+    ref = orc.gateup_split_fp32acc(f32(x), f32(wg), f32(wu))
+    m = orc.error_metrics(f32(h), ref)
+    assert m["rel_fro"] <= REL_FRO_SAME_ROUNDING and m["scaled_max_abs"] <= 2.0 ** -7, m
+
+
+@pytest.mark.parametrize("M,d,F", SHAPES)
+def test_packed_and_split_ops_agree_bitwise(fsw, cuda_dev, M, d, F):
+    x, wg, wu, _ = fsw.inputs.make_mlp_inputs(M, d, F, seed=1)
+    x, wg, wu = x.to(cuda_dev), (wg * 25).to(cuda_dev), (wu * 25).to(cuda_dev)
+    a = fsw.ops.fused_swiglu_gateup_bf16(x, wg, wu)
+    b = fsw.ops.fused_swiglu_bf16(x, fsw.pack.interleave_up_gate(wu, wg))
+    healthy(fsw)
+    assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("M,d,F", SHAPES)
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_down_matches_oracle(fsw, cuda_dev, M, d, F, out_dtype):
+    g = torch.Generator().manual_seed(M * 7 + F)
+    h = torch.randn((M, F), generator=g).to(torch.bfloat16)
+    wd = (torch.randn((d, F), generator=g) / F ** 0.5).to(torch.bfloat16)
+    out = fsw.ops.swiglu_down_bf16(h.to(cuda_dev), wd.to(cuda_dev), out_dtype=out_dtype)
+    healthy(fsw)
+    ref = f32(h) @ f32(wd).T
+    if out_dtype == torch.bfloat16:
+        m = orc.error_metrics(f32(out), orc.bf16_round(ref))
+        assert m["rel_fro"] <= REL_FRO_SAME_ROUNDING and m["scaled_max_abs"] <= 2.0 ** -7, m
+    else:
+        m = orc.error_metrics(f32(out), ref)
+        assert m["rel_fro"] <= 1e-5, m
+
+
+@pytest.mark.parametrize("M,d,F", [(1, 64, 8), (7, 136, 200), (64, 256, 512), (65, 256, 512), (333, 1000, 520)])
+def test_mlp_matches_pipeline_oracle(fsw, cuda_dev, M, d, F):
+    x, wg, wu, wd = fsw.inputs.make_mlp_inputs(M, d, F, seed=9)
+    out = fsw.ops.fused_swiglu_mlp_bf16(x.to(cuda_dev), wg.to(cuda_dev), wu.to(cuda_dev), wd.to(cuda_dev))
+    healthy(fsw)
+    a = [f32(t) for t in (x, wg, wu, wd)]
+    m = orc.error_metrics(f32(out), orc.mlp_bf16_pipeline(*a))
+    assert m["rel_fro"] <= REL_FRO_SAME_ROUNDING, m
+    m2 = orc.error_metrics(f32(out), orc.mlp_fp32(*a))
+    assert m2["rel_fro"] <= REL_FRO_GRADED and m2["scaled_max_abs"] <= SCALED_MAX_ABS, m2
+
+
+# ------------------------------------------------------------------ the benchmark configurations
+def test_config1_full_size_within_published_tolerance(fsw, cuda_dev):
+    """Configuration 1 (M=512, d=1024, F=2816): whole output vs the fp32 expression,
+    max-abs <= 2e-2 and rel-Fro <= 5e-3."""
+    x, wg, wu, wd = fsw.inputs.make_config_inputs("c1_cpu_small")
+    out = fsw.ops.fused_swiglu_mlp_bf16(x.to(cuda_dev), wg.to(cuda_dev), wu.to(cuda_dev), wd.to(cuda_dev))
+    healthy(fsw)
+    m = orc.error_metrics(f32(out), orc.mlp_fp32(*[f32(t) for t in (x, wg, wu, wd)]))
+    assert m["max_abs"] <= MAX_ABS_GRADED and m["rel_fro"] <= REL_FRO_GRADED, m
+
+
+def _rows_to_check(M, n=96, seed=0):
+    rng = np.random.default_rng(seed)
+    edge = [r for r in (0, 1, 127, 128, 129, 255, 256, M - 129, M - 128, M - 2, M - 1) if 0 <= r < M]
+    rand = rng.choice(M, size=min(n, M), replace=False).tolist()
+    return sorted(set(edge + rand))
+
+
+@pytest.mark.parametrize("name", ["c2_llama2_7b_prefill", "c3_llama3_8b_decode_m1", "c3_llama3_8b_decode_m4",
+                                  "c3_llama3_8b_decode_m16", "c3_llama3_8b_decode_m64"])
+def test_full_size_configs_row_subset(fsw, cuda_dev, name):
+    """Full-size single-GPU configurations: the GPU runs all M rows; tile-edge rows and a random
+    sample of rows (all columns) are checked against the fp32 expression on the CPU."""
+    x, wg, wu, wd = fsw.inputs.make_config_inputs(name)
+    xd, wgd, wud, wdd = (t.to(cuda_dev) for t in (x, wg, wu, wd))
+    out = fsw.ops.fused_swiglu_mlp_bf16(xd, wgd, wud, wdd)
+    healthy(fsw)
+    rows = _rows_to_check(x.size(0))
+    ref = orc.mlp_fp32(f32(x[rows]), f32(wg), f32(wu), f32(wd))
+    m = orc.error_metrics(f32(out[rows]), ref)
+    assert m["rel_fro"] <= REL_FRO_GRADED and m["scaled_max_abs"] <= SCALED_MAX_ABS, m
+    # size-independent properties on the full output
+    out2 = fsw.ops.fused_swiglu_mlp_bf16(xd, wgd, wud, wdd)
+    assert torch.equal(out, out2), "not deterministic"
+    if x.size(0) >= 256:
+        perm = torch.randperm(x.size(0), generator=torch.Generator().manual_seed(1)).to(cuda_dev)
+        out_p = fsw.ops.fused_swiglu_mlp_bf16(xd[perm].contiguous(), wgd, wud, wdd)
+        assert torch.equal(out_p, out[perm]), "rows are not independent of their position"
+    out_neg = fsw.ops.fused_swiglu_mlp_bf16(xd, wgd, wud, (-wdd).contiguous())
+    assert torch.equal(out_neg, -out), "not odd in W_down"
+    out_scaled = fsw.ops.fused_swiglu_mlp_bf16(xd, wgd, wud, (wdd * 2).contiguous())
+    assert torch.equal(out_scaled, out * 2), "power-of-two scaling of W_down is not exact"
+    healthy(fsw)
+
+
+@pytest.mark.parametrize("name,world", [("c4_llama3_70b_prefill", 8), ("c5_ragged_13b", 8)])
+def test_tp_shard_partials_sum_to_oracle(fsw, cuda_dev, name, world):
+    """The tensor-parallel configurations on ONE GPU: every rank's shard is run in turn, the fp32
+    partial sums are added in fp32 and rounded once, exactly what the collective does; a row sample
+    is compared with the fp32 expression.  Covers F/8 = 1728 (not a multiple of 128) and ragged M."""
+    max_rows = 640 if name.startswith("c4") else 414  # 414 = 3*128 + 30: same remainder as M = 32414
+    x, wg, wu, wd = fsw.inputs.make_config_inputs(name, max_rows=max_rows)
+    xd = x.to(cuda_dev)
+    acc = torch.zeros((x.size(0), wd.size(0)), dtype=torch.float32, device=cuda_dev)
+    for r in range(world):
+        g, u, dn = fsw.pack.shard_mlp_weights(wg, wu, wd, world, r)
+        acc += fsw.ops.fused_swiglu_mlp_bf16(xd, g.to(cuda_dev), u.to(cuda_dev), dn.to(cuda_dev),
+                                             out_dtype=torch.float32)
+    healthy(fsw)
+    out = torch.empty_like(acc, dtype=torch.bfloat16)
+    import ctypes
+    rc = fsw.capi.lib.fswiglu_cast_f32_to_bf16(ctypes.c_void_p(acc.data_ptr()), ctypes.c_void_p(out.data_ptr()),
+                                                acc.numel(), None)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert torch.equal(out, acc.to(torch.bfloat16)), "cast kernel differs from round-to-nearest-even"
+    rows = _rows_to_check(x.size(0), n=64)
+    ref = orc.mlp_fp32(f32(x[rows]), f32(wg), f32(wu), f32(wd))
+    m = orc.error_metrics(f32(out[rows]), ref)
+    assert m["rel_fro"] <= REL_FRO_GRADED and m["scaled_max_abs"] <= SCALED_MAX_ABS, m
+
+
+# ------------------------------------------------------------------ edges and the boundary
+def test_empty_batch_is_a_no_op(fsw, cuda_dev):
+    x = torch.empty((0, 64), dtype=torch.bfloat16, device=cuda_dev)
+    w = torch.zeros((16, 64), dtype=torch.bfloat16, device=cuda_dev)
+    assert fsw.ops.fused_swiglu_gateup_bf16(x, w, w).shape == (0, 16)
+    assert fsw.ops.fused_swiglu_mlp_bf16(x, w, w, w.t().contiguous()).shape == (0, 64)
+    healthy(fsw)
+
+
+def test_outputs_do_not_write_outside_their_rows_and_columns(fsw, cuda_dev):
+    """Canary-padded outputs (no sanitizer on this pool): strided output views inside a buffer filled
+    with a sentinel; everything outside the view must be untouched."""
+    M, d, F = 200, 136, 264
+    x, wg, wu, wd = fsw.inputs.make_mlp_inputs(M, d, F, seed=4)
+    x, wg, wu, wd = (t.to(cuda_dev) for t in (x, wg, wu, wd))
+    sentinel = 1234.0
+    big = torch.full((M + 16, F + 24), sentinel, dtype=torch.bfloat16, device=cuda_dev)
+    view = big[8:8 + M, 8:8 + F]  # row pitch F+24 (16-byte multiple), base 16 bytes into the row
+    import ctypes
+    rc = fsw.capi.lib.fswiglu_gateup_bf16(ctypes.c_void_p(x.data_ptr()), d, ctypes.c_void_p(wg.data_ptr()), d,
+                                          ctypes.c_void_p(wu.data_ptr()), ctypes.c_void_p(view.data_ptr()), F + 24,
+                                          M, F, d, 0, None)
+    assert rc == 0
+    healthy(fsw)
+    ref = fsw.ops.fused_swiglu_gateup_bf16(x, wg, wu)
+    assert torch.equal(view, ref)
+    mask = torch.ones_like(big, dtype=torch.bool)
+    mask[8:8 + M, 8:8 + F] = False
+    assert bool((big[mask] == sentinel).all())
+    # odd pitch / unaligned base: scalar store path
+    big2 = torch.full((M + 2, F + 3), sentinel, dtype=torch.bfloat16, device=cuda_dev)
+    view2 = big2[1:1 + M, 1:1 + F]
+    rc = fsw.capi.lib.fswiglu_gateup_bf16(ctypes.c_void_p(x.data_ptr()), d, ctypes.c_void_p(wg.data_ptr()), d,
+                                          ctypes.c_void_p(wu.data_ptr()), ctypes.c_void_p(view2.data_ptr()), F + 3,
+                                          M, F, d, 0, None)
+    assert rc == 0
+    healthy(fsw)
+    assert torch.equal(view2, ref)
+    mask2 = torch.ones_like(big2, dtype=torch.bool)
+    mask2[1:1 + M, 1:1 + F] = False
+    assert bool((big2[mask2] == sentinel).all())
+
+
+def test_strided_inputs(fsw, cuda_dev):
+    """Leading dimensions larger than the row length on every TMA-read operand."""
+    M, d, F = 150, 128, 136
+    x, wg, wu, wd = fsw.inputs.make_mlp_inputs(M, d, F, seed=6)
+    xb = torch.zeros((M, d + 64), dtype=torch.bfloat16, device=cuda_dev)
+    xb[:, :d] = x.to(cuda_dev)
+    wb = torch.zeros((2, F, d + 8), dtype=torch.bfloat16, device=cuda_dev)
+    wb[0, :, :d] = wg.to(cuda_dev)
+    wb[1, :, :d] = wu.to(cuda_dev)
+    h = fsw.ops.fused_swiglu_gateup_bf16(xb[:, :d], wb[0, :, :d], wb[1, :, :d])
+    ref = fsw.ops.fused_swiglu_gateup_bf16(x.to(cuda_dev), wg.to(cuda_dev), wu.to(cuda_dev))
+    healthy(fsw)
+    assert torch.equal(h, ref)
+
+
+def test_error_statuses(fsw, cuda_dev):
+    import ctypes
+    lib, capi = fsw.capi.lib, fsw.capi
+    buf = torch.zeros(4096, dtype=torch.bfloat16, device=cuda_dev)
+    p = ctypes.c_void_p(buf.data_ptr())
+    p_odd = ctypes.c_void_p(buf.data_ptr() + 2)
+    assert lib.fswiglu_gateup_bf16(None, 8, p, 8, p, p, 8, 1, 8, 8, 0, None) == capi.ERR_BAD_ARG
+    assert lib.fswiglu_gateup_bf16(p, 8, p, 8, p, p, 8, -1, 8, 8, 0, None) == capi.ERR_BAD_ARG
+    assert lib.fswiglu_gateup_bf16(p, 12, p, 12, p, p, 8, 1, 8, 12, 0, None) == capi.ERR_SHAPE      # d % 8
+    assert lib.fswiglu_gateup_bf16(p, 4, p, 8, p, p, 8, 1, 8, 8, 0, None) == capi.ERR_SHAPE         # ld < d
+    assert lib.fswiglu_gateup_bf16(p_odd, 8, p, 8, p, p, 8, 1, 8, 8, 0, None) == capi.ERR_ALIGNMENT
+    assert lib.fswiglu_gateup_bf16(p, 8, p, 8, p, p, 8, 1, 8, 8, 1, None) == capi.ERR_BAD_ARG       # packed + w_up
+    assert lib.fswiglu_down_bf16(p, 8, p, 8, p, 8, 1, 8, 8, 7, None) == capi.ERR_BAD_ARG            # out dtype
+    assert lib.fswiglu_mlp_bf16(p, 8, p, p, 8, p, 8, p, 8, 0, 1, 8, 8, None, 0, None) == capi.ERR_WORKSPACE
+    with pytest.raises(RuntimeError, match="bfloat16"):
+        fsw.ops.fused_swiglu_bf16(buf.float().view(64, 64), buf.view(64, 64))
+    healthy(fsw)
+
+
+def test_raw_op_writes_half_width_rows_into_full_width_buffer(fsw, cuda_dev):
+    """bench_swiglu.py:91,106 passes C [M, N] and ldC = N: the [M, N/2] result is written densely at
+    row stride N/2 into the first M*N/2 elements, the rest of C stays untouched."""
+    M, K, N = 96, 128, 320
+    g = torch.Generator().manual_seed(3)
+    A = fsw.inputs.kaiming_uniform_bf16(M, K, g).to(cuda_dev)
+    B = fsw.inputs.kaiming_uniform_bf16(N, K, g).to(cuda_dev)
+    C = torch.full((M, N), 7.0, dtype=torch.bfloat16, device=cuda_dev)
+    fsw.ops.swiglu_fwd_bf16(M, N, K, A, K, B, K, C, N)
+    healthy(fsw)
+    want = fsw.ops.fused_swiglu_bf16(A, B)
+    assert torch.equal(C.flatten()[: M * N // 2].view(M, N // 2), want)
+    assert bool((C.flatten()[M * N // 2:] == 7.0).all())
+
+
+def test_host_buffer_entry_point(fsw, cuda_dev):
+    M, d, F = 2500, 256, 520
+    x, wg, wu, wd = fsw.inputs.make_mlp_inputs(M, d, F, seed=8)
+    wg, wu, wd = wg.to(cuda_dev), wu.to(cuda_dev), wd.to(cuda_dev)
+    xh = x.pin_memory()
+    oh = torch.empty((M, d), dtype=torch.bfloat16).pin_memory()
+    ws = fsw.ops.host_workspace(M, d, F, cuda_dev)
+    fsw.ops.fused_swiglu_mlp_bf16_host(xh, wg, wu, wd, oh, ws)
+    healthy(fsw)
+    want = fsw.ops.fused_swiglu_mlp_bf16(x.to(cuda_dev), wg, wu, wd)
+    assert torch.equal(oh, want.cpu())
+
+
+def test_launches_are_counted(fsw, cuda_dev):
+    x, wg, wu, wd = (t.to(cuda_dev) for t in fsw.inputs.make_mlp_inputs(256, 128, 256, seed=1))
+    before = fsw.capi.launch_count()
+    fsw.ops.fused_swiglu_mlp_bf16(x, wg, wu, wd)
+    assert fsw.capi.launch_count() - before >= 1
+    healthy(fsw)
