@@ -7,6 +7,7 @@
 
 #include <atomic>
 #include <cstdint>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -151,6 +152,37 @@ int pick_group_m(int num_m_tiles, int64_t K) {
   return static_cast<int>(g);
 }
 
+// Width of a tile in output columns.  Measured on B200, a tile's main loop is bound by the
+// bytes its CTA pulls from L2 per k-block (A: 128 rows, B: one row per MMA column; about
+// 64 B/clk per SM), not by the MMA itself, so a tile costs time proportional to
+// (128 + MMA columns) and narrower tiles move more bytes per flop.  The persistent schedule
+// gives every CTA ceil(tiles / SMs) tiles, hence cost(width) = waves * (128 + MMA columns).
+// Wide tiles win whenever the grid is full; narrower ones only pay off when the problem
+// would otherwise leave SMs idle.  A narrower width must beat a wider one by 3 % to be
+// chosen.  `mma_per_col` is 1 for the plain GEMM, 2 for the gated one (a gate and an up
+// column per output column).  FSWIGLU_TILE_N overrides the choice, for experiments.
+int pick_tile_n(int num_m_tiles, int64_t n_out, int max_tile, int mma_per_col, int num_sms) {
+  if (const char* env = std::getenv("FSWIGLU_TILE_N")) {
+    const int v = std::atoi(env);
+    if (v >= 16 && v <= max_tile && v % 16 == 0) return v;
+  }
+  int best = max_tile;
+  double best_cost = 1e300;
+  for (int t = max_tile; t >= 32 / mma_per_col; t -= 16) {
+    const int64_t n_tiles = (n_out + t - 1) / t;
+    const int64_t tiles = n_tiles * num_m_tiles;
+    const int64_t waves = (tiles + num_sms - 1) / num_sms;
+    const double cost = static_cast<double>(waves) * (128 + t * mma_per_col);
+    if (cost < best_cost * 0.97) {
+      best_cost = cost;
+      best = t;
+    }
+  }
+  // never wider than the problem (rounded up to the 16-column granule)
+  const int needed = static_cast<int>((n_out + 15) / 16 * 16);
+  return best < needed ? best : (needed < 16 ? 16 : needed);
+}
+
 template <int kMode, bool kOutF32>
 int launch_gemm(const DeviceState& st, const CUtensorMap& ma, const CUtensorMap& mb0,
                 const CUtensorMap& mb1, const GemmParams& p, cudaStream_t stream) {
@@ -165,6 +197,7 @@ int gateup_impl(DeviceState& st, const void* x, int64_t ldx, const void* w0, int
                 const void* w_up, void* h, int64_t ldh, int64_t M, int64_t F, int64_t d,
                 int interleaved, cudaStream_t stream) {
   int rc;
+  if (M == 0) return FSWIGLU_OK;  // empty batch: nothing to read or write, pointers may be null
   if ((rc = check_matrix(x, M, d, ldx, true))) return rc;
   if (interleaved) {
     if (w_up != nullptr) return FSWIGLU_ERR_BAD_ARG;
@@ -174,17 +207,7 @@ int gateup_impl(DeviceState& st, const void* x, int64_t ldx, const void* w0, int
     if ((rc = check_matrix(w_up, F, d, ldw, true))) return rc;
   }
   if ((rc = check_matrix(h, M, F, ldh, false))) return rc;
-  if (M == 0) return FSWIGLU_OK;
 
-  CUtensorMap ma, mb0, mb1;
-  if ((rc = encode_map(&ma, x, M, d, ldx, 128))) return rc;
-  if (interleaved) {
-    if ((rc = encode_map(&mb0, w0, 2 * F, d, ldw, 128))) return rc;
-    mb1 = mb0;
-  } else {
-    if ((rc = encode_map(&mb0, w0, F, d, ldw, 128))) return rc;
-    if ((rc = encode_map(&mb1, w_up, F, d, ldw, 128))) return rc;
-  }
   GemmParams p;
   p.out = h;
   p.ld_out = ldh;
@@ -192,7 +215,17 @@ int gateup_impl(DeviceState& st, const void* x, int64_t ldx, const void* w0, int
   p.n_out = static_cast<int>(F);
   p.K = static_cast<int>(d);
   p.num_m_tiles = static_cast<int>((M + 127) / 128);
-  p.num_n_tiles = static_cast<int>((F + 127) / 128);
+  p.tile_n = pick_tile_n(p.num_m_tiles, F, 128, 2, st.num_sms);
+  p.num_n_tiles = static_cast<int>((F + p.tile_n - 1) / p.tile_n);
+  CUtensorMap ma, mb0, mb1;
+  if ((rc = encode_map(&ma, x, M, d, ldx, 128))) return rc;
+  if (interleaved) {
+    if ((rc = encode_map(&mb0, w0, 2 * F, d, ldw, 2 * p.tile_n))) return rc;
+    mb1 = mb0;
+  } else {
+    if ((rc = encode_map(&mb0, w0, F, d, ldw, p.tile_n))) return rc;
+    if ((rc = encode_map(&mb1, w_up, F, d, ldw, p.tile_n))) return rc;
+  }
   p.group_m = pick_group_m(p.num_m_tiles, d);
   p.vec_ok = (aligned16(h) && ldh % 8 == 0) ? 1 : 0;
   p.status = st.status;
@@ -204,14 +237,11 @@ int down_impl(DeviceState& st, const void* h, int64_t ldh, const void* w_down, i
               int64_t ldo, int64_t M, int64_t d, int64_t F, int out_dtype, cudaStream_t stream) {
   int rc;
   if (out_dtype != FSWIGLU_OUT_BF16 && out_dtype != FSWIGLU_OUT_F32) return FSWIGLU_ERR_BAD_ARG;
+  if (M == 0) return FSWIGLU_OK;
   if ((rc = check_matrix(h, M, F, ldh, true))) return rc;
   if ((rc = check_matrix(w_down, d, F, ldw, true))) return rc;
   if ((rc = check_matrix(out, M, d, ldo, false))) return rc;
-  if (M == 0) return FSWIGLU_OK;
 
-  CUtensorMap ma, mb;
-  if ((rc = encode_map(&ma, h, M, F, ldh, 128))) return rc;
-  if ((rc = encode_map(&mb, w_down, d, F, ldw, 128))) return rc;
   GemmParams p;
   p.out = out;
   p.ld_out = ldo;
@@ -219,7 +249,11 @@ int down_impl(DeviceState& st, const void* h, int64_t ldh, const void* w_down, i
   p.n_out = static_cast<int>(d);
   p.K = static_cast<int>(F);
   p.num_m_tiles = static_cast<int>((M + 127) / 128);
-  p.num_n_tiles = static_cast<int>((d + 255) / 256);
+  p.tile_n = pick_tile_n(p.num_m_tiles, d, 256, 1, st.num_sms);
+  p.num_n_tiles = static_cast<int>((d + p.tile_n - 1) / p.tile_n);
+  CUtensorMap ma, mb;
+  if ((rc = encode_map(&ma, h, M, F, ldh, 128))) return rc;
+  if ((rc = encode_map(&mb, w_down, d, F, ldw, p.tile_n))) return rc;
   p.group_m = pick_group_m(p.num_m_tiles, F);
   const bool f32 = out_dtype == FSWIGLU_OUT_F32;
   p.vec_ok = (aligned16(out) && ldo % (f32 ? 4 : 8) == 0) ? 1 : 0;

@@ -10,9 +10,9 @@
 // operand.  One CTA per SM:
 //
 //   warp 0       TMA producer (one lane): fills a 4-deep ring of
-//                {A 128x64, B 256x64} stages, 48 KiB each
+//                {A 128x64, B up to 256x64} stages, 48 KiB each
 //   warp 1       TMEM owner + MMA issuer (one lane): 4 x tcgen05.mma
-//                (M=128, N=256, K=16) per stage into one of two 256-column
+//                (M=128, N<=256, K=16) per stage into one of two 256-column
 //                TMEM accumulators
 //   warps 2..5   epilogue: tcgen05.ld the finished accumulator (one thread
 //                per output row), apply SiLU(g)*u, round once to bf16, store
@@ -20,12 +20,15 @@
 // The accumulator is double-buffered (2 x 256 of the 512 TMEM columns), so the
 // epilogue of tile t overlaps the main loop of tile t+1.
 //
-// The B tile always holds 256 rows.  What they are depends on the mode:
-//   kPlain             256 consecutive rows of W            -> 256 outputs
-//   kGatedSplit        128 rows of W_gate, then 128 of W_up -> 128 outputs
-//   kGatedInterleaved  256 consecutive rows of the reference's packed W1W3
+// The width of a tile is a run-time choice (`tile_n` output columns, a multiple
+// of 16): the host picks the width that wastes the least of the last wave of
+// the persistent schedule.  The MMA N extent and what the B tile holds depend
+// on the mode:
+//   kPlain             tile_n consecutive rows of W              N = tile_n   (<= 256)
+//   kGatedSplit        tile_n rows of W_gate, then of W_up       N = 2 tile_n (<= 256)
+//   kGatedInterleaved  2 tile_n consecutive rows of the reference's packed W1W3
 //                      (even row = up, odd row = gate; reference
-//                      csrc/SwiGLU/swiglu.cu:376-383)        -> 128 outputs
+//                      csrc/SwiGLU/swiglu.cu:376-383)            N = 2 tile_n (<= 256)
 //
 // Ragged edges cost nothing extra: TMA zero-fills out-of-range rows and
 // K-columns on load, and stores are predicated per row / column.
@@ -43,8 +46,7 @@ constexpr int kBlockK = 64;   // 64 bf16 = one 128-byte swizzle row
 constexpr int kUmmaK = 16;
 constexpr int kStages = 4;
 constexpr int kATileBytes = kBlockM * kBlockK * 2;      // 16 KiB
-constexpr int kBHalfBytes = 128 * kBlockK * 2;          // 16 KiB (one TMA box)
-constexpr int kBTileBytes = 2 * kBHalfBytes;            // 32 KiB
+constexpr int kBTileBytes = kUmmaN * kBlockK * 2;        // 32 KiB (room for the widest tile)
 constexpr int kStageBytes = kATileBytes + kBTileBytes;  // 48 KiB
 constexpr int kTmemCols = 512;
 constexpr int kGemmThreads = 192;
@@ -57,6 +59,7 @@ struct GemmParams {
   long long ld_out;
   int M;
   int n_out;          // number of output columns
+  int tile_n;         // output columns per tile (multiple of 16; <= 256 plain, <= 128 gated)
   int K;
   int num_m_tiles;
   int num_n_tiles;
@@ -86,17 +89,18 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, const GemmParams& p) {
 }
 
 template <bool kOutF32>
-__device__ __forceinline__ void store_chunk32(const GemmParams& p, int row, int col0,
-                                              const float (&v)[32]) {
-  // v holds 32 consecutive output columns of one row, starting at col0.
+__device__ __forceinline__ void store_chunk(const GemmParams& p, int row, int col0, int ncols,
+                                            const float (&v)[32]) {
+  // v holds `ncols` (16 or 32) consecutive output columns of one row, starting at col0.
   if (row >= p.M || col0 >= p.n_out) return;
-  const int valid = min(32, p.n_out - col0);
+  const int valid = min(ncols, p.n_out - col0);
   if constexpr (kOutF32) {
     float* dst = reinterpret_cast<float*>(p.out) + static_cast<long long>(row) * p.ld_out + col0;
-    if (p.vec_ok && valid == 32) {
+    if (p.vec_ok && valid == ncols) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        if (4 * i < ncols)
+          reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
       }
     } else {
 #pragma unroll
@@ -107,15 +111,17 @@ __device__ __forceinline__ void store_chunk32(const GemmParams& p, int row, int 
   } else {
     __nv_bfloat16* dst =
         reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(row) * p.ld_out + col0;
-    if (p.vec_ok && valid == 32) {
+    if (p.vec_ok && valid == ncols) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        uint4 q;
-        q.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
-        q.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
-        q.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
-        q.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
-        reinterpret_cast<uint4*>(dst)[i] = q;
+        if (8 * i < ncols) {
+          uint4 q;
+          q.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
+          q.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
+          q.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
+          q.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
+          reinterpret_cast<uint4*>(dst)[i] = q;
+        }
       }
     } else {
 #pragma unroll
@@ -123,6 +129,18 @@ __device__ __forceinline__ void store_chunk32(const GemmParams& p, int row, int 
         if (i < valid) dst[i] = __float2bfloat16_rn(v[i]);
       }
     }
+  }
+}
+
+// 16 or 32 accumulator columns of this thread's row into r[0, ncols).
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, int ncols, uint32_t (&r)[32]) {
+  if (ncols == 32) {
+    tmem_ld_32x32b_x32(taddr, r);
+  } else {
+    uint32_t lo[16];
+    tmem_ld_32x32b_x16(taddr, lo);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) r[i] = lo[i];
   }
 }
 
@@ -177,6 +195,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 
   const int num_tiles = p.num_m_tiles * p.num_n_tiles;
   const int num_kb = (p.K + kBlockK - 1) / kBlockK;
+  const int umma_n = (kMode == kPlain) ? p.tile_n : 2 * p.tile_n;  // accumulator columns in use
+  const uint32_t stage_tx_bytes = kATileBytes + static_cast<uint32_t>(umma_n) * (kBlockK * 2);
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -188,14 +208,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
         const TileCoord tc = tile_coord(tile, p);
         const int m0 = tc.m_tile * kBlockM;
-        int b0_row, b1_row;
-        if (kMode == kGatedSplit) {
-          b0_row = tc.n_tile * 128;  // rows of W_gate
-          b1_row = tc.n_tile * 128;  // rows of W_up
-        } else {
-          b0_row = tc.n_tile * 256;
-          b1_row = b0_row + 128;
-        }
+        // first B row of this tile: rows of W (plain), of W_gate and W_up (split), or of the
+        // packed W1W3 (interleaved: two rows per output column)
+        const int b_row = tc.n_tile * (kMode == kGatedInterleaved ? 2 * p.tile_n : p.tile_n);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!wd.wait(empty_bar(stage), phase ^ 1u, kSiteProducerEmpty)) {
             alive = false;
@@ -203,10 +218,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
           }
           const uint32_t a_dst = smem_base + stage * kStageBytes;
           const uint32_t b_dst = a_dst + kATileBytes;
-          mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
+          mbar_arrive_expect_tx(full_bar(stage), stage_tx_bytes);
           tma_load_2d(a_dst, &map_a, full_bar(stage), kb * kBlockK, m0);
-          tma_load_2d(b_dst, &map_b0, full_bar(stage), kb * kBlockK, b0_row);
-          tma_load_2d(b_dst + kBHalfBytes, &map_b1, full_bar(stage), kb * kBlockK, b1_row);
+          tma_load_2d(b_dst, &map_b0, full_bar(stage), kb * kBlockK, b_row);
+          if (kMode == kGatedSplit) {
+            // W_up rows go right behind the W_gate rows (tile_n * 128 bytes, a multiple of 1024)
+            tma_load_2d(b_dst + p.tile_n * (kBlockK * 2), &map_b1, full_bar(stage), kb * kBlockK, b_row);
+          }
           issued_mask |= 1u << stage;
           last_parity_mask = (last_parity_mask & ~(1u << stage)) | (phase << stage);
           if (++stage == kStages) {
@@ -234,7 +252,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16_f32(kBlockM, kUmmaN);
+      const uint32_t idesc = umma_idesc_bf16_f32(kBlockM, umma_n);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -299,50 +317,44 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       const uint32_t t_acc = tmem_base + lane_field + static_cast<uint32_t>(acc * kUmmaN);
       const int row = tc.m_tile * kBlockM + quarter * 32 + static_cast<int>(lane);
 
-      if constexpr (kMode == kPlain) {
-        const int col_base = tc.n_tile * 256;
+      const int col_base = tc.n_tile * p.tile_n;
 #pragma unroll 1
-        for (int c = 0; c < 8; ++c) {
-          if (col_base + c * 32 >= p.n_out) break;  // warp-uniform
+      for (int c0 = 0; c0 < p.tile_n; c0 += 32) {
+        if (col_base + c0 >= p.n_out) break;  // warp-uniform: the rest of the tile is past the edge
+        const int ncols = min(32, p.tile_n - c0);  // 32, or 16 for the last chunk of an odd width
+        float v[32];
+        if constexpr (kMode == kPlain) {
           uint32_t r[32];
-          tmem_ld_32x32b_x32(t_acc + c * 32, r);
+          tmem_ld_cols(t_acc + c0, ncols, r);
           tmem_ld_wait();
-          float v[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-          store_chunk32<kOutF32>(p, row, col_base + c * 32, v);
-        }
-      } else if constexpr (kMode == kGatedSplit) {
-        const int col_base = tc.n_tile * 128;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          if (col_base + c * 32 >= p.n_out) break;
+          store_chunk<kOutF32>(p, row, col_base + c0, ncols, v);
+        } else if constexpr (kMode == kGatedSplit) {
           uint32_t g[32], u[32];
-          tmem_ld_32x32b_x32(t_acc + c * 32, g);        // gate columns [0,128)
-          tmem_ld_32x32b_x32(t_acc + 128 + c * 32, u);  // up columns [128,256)
+          tmem_ld_cols(t_acc + c0, ncols, g);             // gate columns [0, tile_n)
+          tmem_ld_cols(t_acc + p.tile_n + c0, ncols, u);  // up columns [tile_n, 2 tile_n)
           tmem_ld_wait();
-          float v[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = silu_mul(__uint_as_float(g[i]), __uint_as_float(u[i]));
-          store_chunk32<false>(p, row, col_base + c * 32, v);
-        }
-      } else {
-        const int col_base = tc.n_tile * 128;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          if (col_base + c * 32 >= p.n_out) break;
+          store_chunk<false>(p, row, col_base + c0, ncols, v);
+        } else {
+          // accumulator column 2j = up (linear), 2j+1 = gate (SiLU)
           uint32_t lo[32], hi[32];
-          tmem_ld_32x32b_x32(t_acc + c * 64, lo);
-          tmem_ld_32x32b_x32(t_acc + c * 64 + 32, hi);
+          tmem_ld_32x32b_x32(t_acc + 2 * c0, lo);
+          if (ncols == 32) {
+            tmem_ld_32x32b_x32(t_acc + 2 * c0 + 32, hi);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) hi[i] = 0u;
+          }
           tmem_ld_wait();
-          float v[32];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            // accumulator column 2j = up (linear), 2j+1 = gate (SiLU)
             v[i] = silu_mul(__uint_as_float(lo[2 * i + 1]), __uint_as_float(lo[2 * i]));
             v[16 + i] = silu_mul(__uint_as_float(hi[2 * i + 1]), __uint_as_float(hi[2 * i]));
           }
-          store_chunk32<false>(p, row, col_base + c * 32, v);
+          store_chunk<false>(p, row, col_base + c0, ncols, v);
         }
       }
       tc_fence_before_sync();
@@ -356,6 +368,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) {
+    __syncwarp();
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
   }
