@@ -419,6 +419,83 @@ int fswiglu_mlp_bf16_host(const void* x_host, const void* w_gate, const void* w_
   return (ok && drained) ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of the whole-MLP call (see include/fswiglu.h for who needs it).
+// The hidden activations go into this fixed array instead of a caller workspace.  In host code
+// the name `g_static_scratch` is only a handle for the runtime, not a device address: the address
+// the kernels need is looked up once per device with cudaGetSymbolAddress and cached.
+// Layout: [0, 256) error word of the bounded device-side waits (zero at load time),
+//         [256, 256 + FSWIGLU_STATIC_SCRATCH_BYTES) hidden activations h, row pitch F.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kStaticHeaderBytes = 256;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticHeaderBytes + FSWIGLU_STATIC_SCRATCH_BYTES];
+
+struct StaticState {
+  bool ready = false;
+  DeviceState dev;          // num_sms + status pointer (into the static array), no owned memory
+  unsigned char* base = nullptr;
+};
+StaticState g_static[kMaxDevices];
+
+// Once per device, with that device current: capability check, address of the array, shared-memory
+// opt-in of the kernels.  Nothing here allocates device memory.
+int static_state(StaticState** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return FSWIGLU_ERR_NO_DEVICE;
+  if (dev < 0 || dev >= kMaxDevices) return FSWIGLU_ERR_NO_DEVICE;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  StaticState& st = g_static[dev];
+  if (!st.ready) {
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return FSWIGLU_ERR_NO_DEVICE;
+    if (prop.major != 10) return FSWIGLU_ERR_NO_DEVICE;
+    if (g_encode == nullptr) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult q;
+      if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+          fn == nullptr) {
+        return FSWIGLU_ERR_CUDA;
+      }
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) return FSWIGLU_ERR_CUDA;
+    cudaError_t e = cudaSuccess;
+    e = e ? e : opt_in_smem(gemm_tcgen05_kernel<kPlain, false>, kGemmSmemBytes);
+    e = e ? e : opt_in_smem(gemm_tcgen05_kernel<kPlain, true>, kGemmSmemBytes);
+    e = e ? e : opt_in_smem(gemm_tcgen05_kernel<kGatedSplit, false>, kGemmSmemBytes);
+    if (e != cudaSuccess) return FSWIGLU_ERR_CUDA;
+    st.base = static_cast<unsigned char*>(ptr);
+    st.dev.num_sms = prop.multiProcessorCount;
+    st.dev.status = reinterpret_cast<uint32_t*>(st.base);
+    st.dev.ready = true;
+    st.ready = true;
+  }
+  *out = &st;
+  return FSWIGLU_OK;
+}
+
+}  // namespace
+
+int fswiglu_mlp_bf16_static(const void* x, int64_t ldx, const void* w_gate, const void* w_up,
+                            int64_t ldw_gu, const void* w_down, int64_t ldw_d, void* out, int64_t ldo,
+                            int out_dtype, int64_t M, int64_t d, int64_t F, void* stream) {
+  if (M < 0 || F <= 0 || d <= 0) return FSWIGLU_ERR_BAD_ARG;
+  if (M == 0) return FSWIGLU_OK;
+  // reject before touching the device: the hidden activations must fit the built-in array
+  if (static_cast<uint64_t>(M) > FSWIGLU_STATIC_SCRATCH_BYTES / 2u / static_cast<uint64_t>(F)) {
+    return FSWIGLU_ERR_TOO_LARGE;
+  }
+  StaticState* st = nullptr;
+  if (int rc = static_state(&st)) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  void* h = st->base + kStaticHeaderBytes;
+  if (int rc = gateup_impl(st->dev, x, ldx, w_gate, ldw_gu, w_up, h, F, M, F, d, 0, s)) return rc;
+  return down_impl(st->dev, h, F, w_down, ldw_d, out, ldo, M, d, F, out_dtype, s);
+}
+
 int fswiglu_cast_f32_to_bf16(const void* src, void* dst, int64_t n, void* stream) {
   if (n < 0 || (n > 0 && (src == nullptr || dst == nullptr))) return FSWIGLU_ERR_BAD_ARG;
   if (n == 0) return FSWIGLU_OK;
@@ -464,6 +541,8 @@ const char* fswiglu_status_string(int status) {
     case FSWIGLU_ERR_WATCHDOG: return "device-side wait exceeded its limit";
     case FSWIGLU_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
     case FSWIGLU_ERR_NO_DEVICE: return "current device is not an sm_100 GPU";
+    case FSWIGLU_ERR_TOO_LARGE:
+      return "M * F * 2 bytes exceeds the 32 MiB scratch built into fswiglu_mlp_bf16_static";
     default: return "unknown status";
   }
 }

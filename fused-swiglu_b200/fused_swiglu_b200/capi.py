@@ -20,6 +20,7 @@ ERR_CUDA = -4
 ERR_WATCHDOG = -5
 ERR_WORKSPACE = -6
 ERR_NO_DEVICE = -7
+ERR_TOO_LARGE = -8
 
 OUT_BF16 = 0
 OUT_F32 = 1
@@ -34,6 +35,7 @@ SIGNATURES = {
     "fswiglu_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "fswiglu_mlp_bf16_host": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _sz, _vp]),
     "fswiglu_host_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "fswiglu_mlp_bf16_static": (_int, [_vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _int, _i64, _i64, _i64, _vp]),
     "fswiglu_cast_f32_to_bf16": (_int, [_vp, _vp, _i64, _vp]),
     "fswiglu_device_status": (_int, [ctypes.POINTER(ctypes.c_uint32), _vp]),
     "fswiglu_status_string": (ctypes.c_char_p, [_int]),

@@ -37,7 +37,8 @@ enum {
   FSWIGLU_ERR_CUDA = -4,       /* CUDA runtime / driver call or kernel launch failed    */
   FSWIGLU_ERR_WATCHDOG = -5,   /* a bounded device-side wait gave up (see device_status)*/
   FSWIGLU_ERR_WORKSPACE = -6,  /* workspace missing or smaller than workspace_bytes()   */
-  FSWIGLU_ERR_NO_DEVICE = -7   /* current device is not compute capability 10.x         */
+  FSWIGLU_ERR_NO_DEVICE = -7,  /* current device is not compute capability 10.x         */
+  FSWIGLU_ERR_TOO_LARGE = -8   /* problem exceeds the built-in scratch of the _static call */
 };
 
 /* Output element type of the down projection. */
@@ -96,6 +97,34 @@ int fswiglu_mlp_bf16_host(const void* x_host, const void* w_gate, const void* w_
                           const void* w_down, void* out_host, int64_t M, int64_t d, int64_t F,
                           void* workspace, size_t workspace_bytes, void* stream);
 size_t fswiglu_host_workspace_bytes(int64_t M, int64_t d, int64_t F);
+
+/*
+ * Whole MLP forward for hosts that must not allocate device memory.  This entry point has no
+ * counterpart in the reference; it exists for callers of this library that cannot call cudaMalloc
+ * at all, or not where they call us: a serving process that hands the whole GPU to its own memory
+ * pool when it starts (so a later cudaMalloc fails or fragments the pool), or a latency-critical loop
+ * that cannot tolerate the device-wide synchronisation an allocation may cause.  It computes exactly
+ * what fswiglu_mlp_bf16 computes (always with the tiled tensor-core kernels), but the hidden
+ * activations h [M, F] live in a fixed array built into the library image instead of a caller
+ * workspace, and the call itself performs no cudaMalloc / cudaFree and calls no allocating library
+ * routine.
+ *
+ *   - Limit: M * F * 2 bytes must not exceed FSWIGLU_STATIC_SCRATCH_BYTES (32 MiB: e.g. M = 1024 at
+ *     F = 14336, or M = 512 at F = 28672); beyond it the call returns FSWIGLU_ERR_TOO_LARGE and
+ *     launches nothing.  Every GPU that loads the library carries the array until the process exits.
+ *   - The first call on each device looks the array's device address up (and opts the kernels in to
+ *     their shared-memory size); make that first call before any stream capture begins.
+ *   - All calls on a device share the one array and it keeps the previous call's contents.  Nothing in
+ *     it needs to start at zero (h is fully rewritten before it is read; the error word next to it is
+ *     zero when the library is loaded and, by design, stays set after a device-side time-out).  Two
+ *     calls whose kernels overlap on the GPU (different streams, no ordering between them) race on
+ *     the array and produce garbage: order them.
+ *   - The device-side watchdog of this entry point is separate from fswiglu_device_status().
+ */
+#define FSWIGLU_STATIC_SCRATCH_BYTES (32u << 20)
+int fswiglu_mlp_bf16_static(const void* x, int64_t ldx, const void* w_gate, const void* w_up,
+                            int64_t ldw_gu, const void* w_down, int64_t ldw_d, void* out, int64_t ldo,
+                            int out_dtype, int64_t M, int64_t d, int64_t F, void* stream);
 
 /*
  * dst[i] = bf16(src[i]) for n contiguous elements (round to nearest even): the single rounding after
