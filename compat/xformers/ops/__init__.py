@@ -1,0 +1,1 @@
+"""Import-only stand-in for xformers (see compat/README.md)."""

@@ -142,13 +142,17 @@ int check_matrix(const void* p, int64_t rows, int64_t cols, int64_t ld, bool tma
   return FSWIGLU_OK;
 }
 
-// How many 128-row M-tiles share one sweep over N: sized so that the slab of A they
-// cover (group_m * 128 rows * K bf16) stays comfortably inside the 126 MB L2.
+// How many 128-row M-tiles share one sweep over N.  B is re-read from DRAM once per group of
+// M-tiles while the group's slab of A (group_m * 128 rows * K bf16) is read once and then
+// served from the 126 MB L2, so DRAM traffic = |A| + |B| * groups: use as few groups as an
+// 80 MB slab budget allows, of equal size.
 int pick_group_m(int num_m_tiles, int64_t K) {
-  const int64_t slab_budget = 32ll << 20;
+  const int64_t slab_budget = 80ll << 20;
   int64_t g = slab_budget / (128 * K * 2);
   if (g < 1) g = 1;
   if (g > num_m_tiles) g = num_m_tiles;
+  const int64_t groups = (num_m_tiles + g - 1) / g;
+  g = (num_m_tiles + groups - 1) / groups;
   return static_cast<int>(g);
 }
 

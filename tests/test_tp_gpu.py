@@ -1,0 +1,102 @@
+"""Tensor-parallel forward on GPUs.  With one GPU the world-size-1 path (slab schedule, fp32
+partials, single rounding on the device) is checked; with two or more GPUs, 2 ranks (and 4 when
+available) run over NCCL and every rank's result is compared with the CPU oracle and with the
+single-GPU kernel path."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def f32(t):
+    return t.detach().float().cpu().numpy()
+
+
+@pytest.mark.parametrize("mode", ["allreduce", "rs_ag"])
+@pytest.mark.parametrize("M", [1, 100, 1000])
+def test_world_size_one_matches_fused_op(cuda_dev, mode, M):
+    import fused_swiglu_b200 as fsw
+    from fused_swiglu_b200.tp import TensorParallelSwiGLU
+
+    x, wg, wu, wd = (t.to(cuda_dev) for t in fsw.inputs.make_mlp_inputs(M, 256, 520, seed=3))
+    tp = TensorParallelSwiGLU(wg, wu, wd, n_slabs=3, mode=mode)
+    out = tp.forward(x)
+    want = fsw.ops.fused_swiglu_mlp_bf16(x, wg, wu, wd)
+    torch.cuda.synchronize()
+    assert out.shape == want.shape and out.dtype == torch.bfloat16
+    # fp32 partial then one rounding == direct bf16 output of the same accumulator
+    assert torch.equal(out, want)
+    assert fsw.capi.device_status() == 0
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, mode, M, q):
+    for p in (ROOT, os.path.join(ROOT, "fused-swiglu_b200")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    import datetime
+
+    import torch.distributed as dist
+
+    import fused_swiglu_b200 as fsw
+    from fused_swiglu_b200.tp import TensorParallelSwiGLU
+    from oracle import swiglu_oracle as orc
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=120))
+    try:
+        x, wg, wu, wd = fsw.inputs.make_mlp_inputs(M, 512, 1736, seed=4)  # 1736 / 8 = 217: ragged shards
+        tp = TensorParallelSwiGLU.from_full(wg, wu, wd, dev, n_slabs=3, mode=mode)
+        out = tp.forward(x.to(dev))
+        out2 = tp.forward(x.to(dev))
+        torch.cuda.synchronize()
+        ref = orc.mlp_fp32(f32(x), f32(wg), f32(wu), f32(wd))
+        m = orc.error_metrics(f32(out), ref)
+        gathered = [torch.empty_like(out) for _ in range(world)]
+        dist.all_gather(gathered, out)
+        same = all(torch.equal(g, out) for g in gathered) and torch.equal(out, out2)
+        q.put((rank, "ok", m["rel_fro"], m["scaled_max_abs"], same, fsw.capi.device_status()))
+    except Exception as e:  # noqa: BLE001
+        q.put((rank, "error", repr(e)[:300], 0.0, False, -1))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("mode", ["allreduce", "rs_ag"])
+def test_nccl_ranks_match_oracle(world, mode):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, mode, 777, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted(q.get(timeout=300) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+    for rank, status, rel_fro, scaled, same, wd_status in results:
+        assert status == "ok", results
+        assert rel_fro <= 5e-3 and scaled <= 8e-3, results
+        assert same, "ranks disagree or the forward is not repeatable"
+        assert wd_status == 0
