@@ -270,9 +270,9 @@ int down_impl(DeviceState& st, const void* h, int64_t ldh, const void* w_down, i
 
 size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// Small-batch MLP: one cooperative stream-K weight-streaming launch (gate-up, hand-over, down)
-// plus one tiny memset of the hand-over and per-row-block arrival counters.  `h` receives the bf16 hidden activations,
-// `scratch` the counters and fp32 partial tiles (decode_workspace_bytes).
+// Small-batch MLP: one cooperative weight-streaming launch (gate-up, hand-over, down) plus a
+// 4-byte memset of the hand-over counter.  `h` receives the bf16 hidden activations, `scratch`
+// holds the counter (decode_workspace_bytes).
 int decode_impl(DeviceState& st, const void* x, int64_t ldx, const void* w_gate, const void* w_up, int64_t ldw_gu,
                 const void* w_down, int64_t ldw_d, void* out, int64_t ldo, int out_dtype, int64_t M, int64_t d,
                 int64_t F, void* h, void* scratch, cudaStream_t stream) {
@@ -285,68 +285,44 @@ int decode_impl(DeviceState& st, const void* x, int64_t ldx, const void* w_gate,
   if ((rc = check_matrix(out, M, d, ldo, false))) return rc;
 
   const int n_pad = decode_pad_tokens(M);
-  const int rb1 = static_cast<int>((F + 127) / 128), kb1 = static_cast<int>((d + 63) / 64);
   const int rb2 = static_cast<int>((d + 127) / 128), kb2 = static_cast<int>((F + 63) / 64);
   uint8_t* ws = static_cast<uint8_t*>(scratch);
-  unsigned int* counters = reinterpret_cast<unsigned int*>(ws);  // [0] hand-over, then per row-block
-  const size_t counters_bytes = decode_counter_bytes(d, F);
-  float* partials1 = reinterpret_cast<float*>(ws + counters_bytes);
-  float* partials2 = reinterpret_cast<float*>(
-      ws + counters_bytes +
-      decode_round256(static_cast<size_t>(rb1) * kDecMaxSegments * 128 * (2 * n_pad) * sizeof(float)));
-  if (cudaMemsetAsync(counters, 0, static_cast<size_t>(1 + rb1 + rb2) * sizeof(unsigned int), stream) !=
-      cudaSuccess)
+  unsigned int* counters = reinterpret_cast<unsigned int*>(ws);  // [0] hand-over, then one per row-block
+  if (cudaMemsetAsync(counters, 0, static_cast<size_t>(1 + rb2) * sizeof(unsigned int), stream) != cudaSuccess)
     return FSWIGLU_ERR_CUDA;
 
-  CUtensorMap m_gate, m_up, m_x, m_down, m_h;
-  if ((rc = encode_map(&m_gate, w_gate, F, d, ldw_gu, 128))) return rc;
-  if ((rc = encode_map(&m_up, w_up, F, d, ldw_gu, 128))) return rc;
-  if ((rc = encode_map(&m_x, x, M, d, ldx, n_pad))) return rc;
-  if ((rc = encode_map(&m_down, w_down, d, F, ldw_d, 128))) return rc;
-  if ((rc = encode_map(&m_h, h, M, F, F, n_pad))) return rc;
-
   DecodeParams p;
-  p.ph[0].out = h;
-  p.ph[0].ld_out = F;
-  p.ph[0].partials = partials1;
-  p.ph[0].counters = counters + 1;
-  p.ph[0].n_rows = static_cast<int>(F);
-  p.ph[0].row_blocks = rb1;
-  p.ph[0].k_blocks = kb1;
-  p.ph[0].out_f32 = 0;
-  p.ph[1].out = out;
-  p.ph[1].ld_out = ldo;
-  p.ph[1].partials = partials2;
-  p.ph[1].counters = counters + 1 + rb1;
-  p.ph[1].n_rows = static_cast<int>(d);
-  p.ph[1].row_blocks = rb2;
-  p.ph[1].k_blocks = kb2;
-  p.ph[1].out_f32 = out_dtype == FSWIGLU_OUT_F32 ? 1 : 0;
+  int used1 = 0;
+  decode_plan_rows(F, st.num_sms, &p.tile_rows, &p.tiles_per_cta, &used1);
+  p.h = h;
+  p.F = static_cast<int>(F);
+  p.k_blocks1 = static_cast<int>((d + 63) / 64);
+  p.out = out;
+  p.ld_out = ldo;
+  p.d = static_cast<int>(d);
+  p.row_blocks2 = rb2;
+  p.k_blocks2 = kb2;
+  p.out_f32 = out_dtype == FSWIGLU_OUT_F32 ? 1 : 0;
+  p.partials = reinterpret_cast<float*>(ws + decode_counter_bytes(d));
+  p.counters = counters + 1;
   p.handover = counters;
   p.M = static_cast<int>(M);
   p.n_pad = n_pad;
   p.status = st.status;
-#ifdef FSW_DECODE_TRACE
-  static unsigned long long* trace_buf = nullptr;
-  if (trace_buf == nullptr) cudaMalloc(&trace_buf, 256 * 8 * sizeof(unsigned long long));
-  p.trace = trace_buf;
-  if (const char* path = std::getenv("FSWIGLU_DECODE_TRACE_DUMP")) {
-    // dump the stamps of the PREVIOUS launch, then clear
-    static unsigned long long host[256 * 8];
-    cudaStreamSynchronize(stream);
-    cudaMemcpy(host, trace_buf, sizeof(host), cudaMemcpyDeviceToHost);
-    if (FILE* f = std::fopen(path, "w")) {
-      for (int c = 0; c < 256; ++c) {
-        for (int k = 0; k < 8; ++k) std::fprintf(f, "%llu ", host[c * 8 + k]);
-        std::fprintf(f, "\n");
-      }
-      std::fclose(f);
-    }
+
+  CUtensorMap m_gate, m_up, m_x, m_down, m_h;
+  if ((rc = encode_map(&m_gate, w_gate, F, d, ldw_gu, p.tile_rows))) return rc;
+  if ((rc = encode_map(&m_up, w_up, F, d, ldw_gu, p.tile_rows))) return rc;
+  if ((rc = encode_map(&m_x, x, M, d, ldx, n_pad))) return rc;
+  if ((rc = encode_map(&m_down, w_down, d, F, ldw_d, 128))) return rc;
+  if ((rc = encode_map(&m_h, h, M, F, F, n_pad))) return rc;
+  // every CTA takes part in both phases: the grid must not exceed what phase 2 can split into
+  const int grid = std::max(1, std::min(st.num_sms, decode_grid_limit(rb2, kb2, st.num_sms)));
+  if (grid < used1) decode_plan_rows(F, grid, &p.tile_rows, &p.tiles_per_cta, &used1);
+  if (grid < st.num_sms) {
+    if ((rc = encode_map(&m_gate, w_gate, F, d, ldw_gu, p.tile_rows))) return rc;
+    if ((rc = encode_map(&m_up, w_up, F, d, ldw_gu, p.tile_rows))) return rc;
   }
-#endif
-  int grid = st.num_sms;
-  grid = std::min(grid, decode_grid_limit(rb1, kb1, st.num_sms));
-  grid = std::min(grid, decode_grid_limit(rb2, kb2, st.num_sms));
   // Cooperative launch: the phase hand-over needs every CTA resident at the same time.
   void* args[] = {&m_gate, &m_up, &m_down, &m_x, &m_h, &p};
   const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(decode_fused_kernel), dim3(grid),

@@ -7,23 +7,28 @@
 //   (grid-wide hand-over: every CTA has finished writing its part of h)
 //   phase 2   out[M,d] = h Wd^T
 //
-//   * swap-AB: the WEIGHT tile (128 rows x 64 k) is the MMA's M operand and the
-//     tokens (padded to N = 16/32/64) are its N operand, so a 128-lane TMEM
-//     accumulator holds 128 weight rows x N tokens and no tensor-core work is
-//     spent on padding M up to 128;
-//   * stream-K: the (row-block, k-block) units of each phase are cut into equal
-//     contiguous ranges, one per SM, so every SM streams the same number of
-//     bytes however F/128 divides by the SM count;
-//   * two TMA rings per SM: 11 x 16 KiB weight tiles (evict-first L2 hint) and
-//     4 x 8 KiB token tiles (x in phase 1, h in phase 2).  The weight producer
-//     never waits for the hand-over: while the last row-blocks of phase 1 are
-//     being reduced it already fills its ring with W_down tiles, so the
-//     hand-over costs no HBM idle time;
-//   * row-blocks whose K range spans several CTAs are combined through fp32
-//     partial tiles in a workspace; the CTA that arrives last (an atomic
-//     counter per row-block, no spinning) sums the partials in FIXED segment
-//     order, so results do not depend on timing, then applies SiLU(g)*u (the
-//     gate is non-linear: it must see complete sums) and writes h / out;
+//   * swap-AB: the WEIGHT tile (up to 128 rows x 64 k) is the MMA's M operand and
+//     the tokens (padded to N = 16/32/64) are its N operand, so a TMEM
+//     accumulator holds weight rows x tokens and no tensor-core work is spent on
+//     padding M up to 128;
+//   * phase 1 is a ROW split without split-K: each SM owns ceil(F / SMs)
+//     consecutive rows of W_gate and W_up (97 of 14336 ...) for the whole
+//     reduction length d.  A TMA box may have any number of rows, so the split
+//     is even to within one row; the MMA still runs at M = 128 and accumulator
+//     lanes past the tile are never read.  No partial sums: when the last byte
+//     has arrived the tail is one TMEM read, SiLU(g)*u and the h stores, so the
+//     hand-over to phase 2 follows the weight stream by a few microseconds;
+//   * phase 2 is STREAM-K: W_down has few rows and a long reduction, so its
+//     (128-row block, k-block) units are cut into equal contiguous ranges, one
+//     per SM (full 128-row MMAs, and each SM reads only its own k-range of h).
+//     Row-blocks whose K range spans several CTAs are combined through fp32
+//     partial tiles in a workspace; the CTA that arrives last (an atomic counter
+//     per row-block, no spinning) sums them in FIXED segment order, so results
+//     do not depend on timing;
+//   * two TMA rings per SM: 11 x 16 KiB weight slots (evict-first L2 hint) and a
+//     32 KiB ring of token tiles (x in phase 1, h in phase 2).  The weight
+//     producer never waits for the hand-over: while h is being completed it
+//     already fills its ring with W_down tiles;
 //   * the only spin in the kernel is the token-tile producer waiting for the
 //     hand-over counter; it is bounded like every other wait, and the kernel is
 //     launched cooperatively so that all CTAs are resident together.
@@ -40,40 +45,35 @@ namespace fsw {
 
 constexpr int kDecodeMaxTokens = 64;
 constexpr int kDecThreads = 224;              // 7 warps: W producer, MMA, 4 epilogue, token-tile producer
-constexpr int kDecWTileBytes = 128 * 64 * 2;  // 16 KiB: 128 weight rows x 64 k
-constexpr int kDecXTileBytes = 64 * 64 * 2;   // 8 KiB: up to 64 tokens x 64 k
+constexpr int kDecWSlotBytes = 16384;
 constexpr int kDecWSlots = 11;
-constexpr int kDecXSlots = 4;
-constexpr int kDecMaxSegments = 8;            // partial tiles kept per row-block
-constexpr int kDecSmemBytes = kDecWSlots * kDecWTileBytes + kDecXSlots * kDecXTileBytes + 1024 + 512;
+constexpr int kDecXRingBytes = 32768;
+constexpr int kDecMaxXSlots = 16;
+constexpr int kDecSmemBytes = kDecWSlots * kDecWSlotBytes + kDecXRingBytes + 1024 + 1024;
 
-struct DecodePhase {
-  void* out;              // phase 1: h bf16 [M, n_rows]; phase 2: out bf16/fp32 [M, n_rows]
-  long long ld_out;
-  float* partials;        // [row_blocks][kDecMaxSegments][128][acc_cols] fp32
-  unsigned int* counters; // [row_blocks], zero on entry
-  int n_rows;             // weight rows = output features (F, then d)
-  int row_blocks;         // ceil(n_rows / 128)
-  int k_blocks;           // ceil(K / 64) with K = d, then F
-  int out_f32;
-};
+constexpr int kDecMaxSegments = 8;  // partial tiles kept per row-block of phase 2
 
 struct DecodeParams {
-  DecodePhase ph[2];
+  // phase 1 (row split): h[M, F] = silu(x Wg^T) * (x Wu^T)
+  void* h;            // bf16 [M, F], row pitch F
+  int F;              // rows of W_gate / W_up
+  int k_blocks1;      // ceil(d / 64)
+  int tile_rows;      // weight rows per tile (1..128) = rows of one TMA box
+  int tiles_per_cta;  // consecutive tiles each CTA owns
+  // phase 2 (stream-K): out[M, d] = h Wd^T
+  void* out;          // bf16 / fp32 [M, d]
+  long long ld_out;
+  int d;              // rows of W_down
+  int row_blocks2;    // ceil(d / 128)
+  int k_blocks2;      // ceil(F / 64)
+  int out_f32;
+  float* partials;        // [row_blocks2][kDecMaxSegments][128][n_pad] fp32
+  unsigned int* counters; // [row_blocks2], zero on entry
   unsigned int* handover; // one counter, zero on entry: CTAs that finished phase 1
   int M;                  // tokens (<= 64)
   int n_pad;              // tokens padded to 16 / 32 / 64 (the MMA N extent)
   uint32_t* status;
-#ifdef FSW_DECODE_TRACE
-  unsigned long long* trace;  // [grid][8] globaltimer stamps, debug builds only
-#endif
 };
-
-#ifdef FSW_DECODE_TRACE
-#define FSW_TRACE(slot) do { if (p.trace) p.trace[blockIdx.x * 8 + (slot)] = global_timer_ns(); } while (0)
-#else
-#define FSW_TRACE(slot) do { } while (0)
-#endif
 
 // First unit of CTA c when `units` units are cut into `ctas` contiguous ranges.
 __host__ __device__ inline long long dec_range_start(long long c, long long units, long long ctas) {
@@ -100,36 +100,37 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t w_ring = smem_base;
-  const uint32_t x_ring = smem_base + kDecWSlots * kDecWTileBytes;
-  const uint32_t bar_base = x_ring + kDecXSlots * kDecXTileBytes;
+  const uint32_t x_ring = smem_base + kDecWSlots * kDecWSlotBytes;
+  const uint32_t bar_base = x_ring + kDecXRingBytes;
   auto w_full = [&](int s) { return bar_base + 8u * s; };
   auto w_empty = [&](int s) { return bar_base + 8u * (kDecWSlots + s); };
   auto x_full = [&](int s) { return bar_base + 8u * (2 * kDecWSlots + s); };
-  auto x_empty = [&](int s) { return bar_base + 8u * (2 * kDecWSlots + kDecXSlots + s); };
-  constexpr int kBarsBeforeTmem = 2 * kDecWSlots + 2 * kDecXSlots;
+  auto x_empty = [&](int s) { return bar_base + 8u * (2 * kDecWSlots + kDecMaxXSlots + s); };
+  constexpr int kBarsBeforeTmem = 2 * kDecWSlots + 2 * kDecMaxXSlots;
   auto tfull_bar = [&](int a) { return bar_base + 8u * (kBarsBeforeTmem + a); };
   auto tempty_bar = [&](int a) { return bar_base + 8u * (kBarsBeforeTmem + 2 + a); };
   const uint32_t drain_bar = bar_base + 8u * (kBarsBeforeTmem + 4);
   uint8_t* generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
   volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(
-      generic_base + kDecWSlots * kDecWTileBytes + kDecXSlots * kDecXTileBytes + 8 * (kBarsBeforeTmem + 5));
+      generic_base + kDecWSlots * kDecWSlotBytes + kDecXRingBytes + 8 * (kBarsBeforeTmem + 5));
   volatile uint32_t* abort_flag = tmem_ptr_slot + 1;
-  volatile uint32_t* last_flag = tmem_ptr_slot + 2;
-  volatile uint32_t* epi_ok = tmem_ptr_slot + 3;  // two entries, alternating per segment
+  volatile uint32_t* epi_ok = tmem_ptr_slot + 2;  // two entries, alternating per tile / segment
+  volatile uint32_t* last_flag = tmem_ptr_slot + 4;
 
   const int warp = threadIdx.x >> 5;
   const uint32_t lane = lane_id();
   const Watchdog wd{abort_flag, p.status};
 
   constexpr int kAccStride = 128;  // TMEM columns per accumulator stage (2 stages)
-  const uint32_t x_tile_tx = static_cast<uint32_t>(p.n_pad) * 128u;
+  const uint32_t x_slot_bytes = static_cast<uint32_t>(p.n_pad) * 128u;
+  const int x_slots = kDecXRingBytes / static_cast<int>(x_slot_bytes);  // 16 / 8 / 4
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kDecWSlots; ++s) {
       mbar_init(w_full(s), 1);
       mbar_init(w_empty(s), 1);
     }
-    for (int s = 0; s < kDecXSlots; ++s) {
+    for (int s = 0; s < kDecMaxXSlots; ++s) {
       mbar_init(x_full(s), 1);
       mbar_init(x_empty(s), 1);
     }
@@ -155,15 +156,15 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr_slot;
-  if (threadIdx.x == 0) FSW_TRACE(0);
 
-  // This CTA's unit range in each phase.
-  long long u_begin[2], u_end[2], units[2];
-  for (int q = 0; q < 2; ++q) {
-    units[q] = static_cast<long long>(p.ph[q].row_blocks) * p.ph[q].k_blocks;
-    u_begin[q] = dec_range_start(blockIdx.x, units[q], gridDim.x);
-    u_end[q] = dec_range_start(blockIdx.x + 1, units[q], gridDim.x);
-  }
+  // phase 1: first weight row of this CTA's i-th tile (>= F: the tile does not exist)
+  auto tile_row0 = [&](int i) {
+    return (static_cast<long long>(blockIdx.x) * p.tiles_per_cta + i) * p.tile_rows;
+  };
+  // phase 2: this CTA's contiguous range of (row-block, k-block) units
+  const long long units2 = static_cast<long long>(p.row_blocks2) * p.k_blocks2;
+  const long long u_begin = dec_range_start(blockIdx.x, units2, gridDim.x);
+  const long long u_end = dec_range_start(blockIdx.x + 1, units2, gridDim.x);
 
   if (warp == 0) {
     // ------------------- weight-tile producer: never waits for the hand-over -------------------
@@ -173,10 +174,10 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
       uint32_t phase = 0;
       uint32_t issued_mask = 0, last_parity_mask = 0;
       bool alive = true;
-      auto push = [&](const CUtensorMap* map, int x, int y) -> bool {
+      auto fill = [&](const CUtensorMap* map, int x, int y, uint32_t bytes) -> bool {
         if (!wd.wait(w_empty(slot), phase ^ 1u, kSiteProducerEmpty)) return false;
-        mbar_arrive_expect_tx(w_full(slot), kDecWTileBytes);
-        tma_load_2d_hint(w_ring + slot * kDecWTileBytes, map, w_full(slot), x, y, stream_once);
+        mbar_arrive_expect_tx(w_full(slot), bytes);
+        tma_load_2d_hint(w_ring + slot * kDecWSlotBytes, map, w_full(slot), x, y, stream_once);
         issued_mask |= 1u << slot;
         last_parity_mask = (last_parity_mask & ~(1u << slot)) | (phase << slot);
         if (++slot == kDecWSlots) {
@@ -185,17 +186,19 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
         }
         return true;
       };
-      for (int q = 0; q < 2 && alive; ++q) {
-        const int kbs = p.ph[q].k_blocks;
-        for (long long u = u_begin[q]; u < u_end[q] && alive; ++u) {
-          const int rb = static_cast<int>(u / kbs);
-          const int kb = static_cast<int>(u - static_cast<long long>(rb) * kbs);
-          if (q == 0) {
-            alive = push(&map_gate, kb * 64, rb * 128) && push(&map_up, kb * 64, rb * 128);
-          } else {
-            alive = push(&map_down, kb * 64, rb * 128);
-          }
+      const uint32_t tile_bytes = static_cast<uint32_t>(p.tile_rows) * 128u;
+      for (int i = 0; i < p.tiles_per_cta && alive; ++i) {
+        const long long row0 = tile_row0(i);
+        if (row0 >= p.F) break;
+        for (int kb = 0; kb < p.k_blocks1 && alive; ++kb) {
+          alive = fill(&map_gate, kb * 64, static_cast<int>(row0), tile_bytes) &&
+                  fill(&map_up, kb * 64, static_cast<int>(row0), tile_bytes);
         }
+      }
+      for (long long u = u_begin; u < u_end && alive; ++u) {
+        const int rb = static_cast<int>(u / p.k_blocks2);
+        const int kb = static_cast<int>(u - static_cast<long long>(rb) * p.k_blocks2);
+        alive = fill(&map_down, kb * 64, rb * 128, 128u * 128u);
       }
       if (wd.aborted()) {
         for (int s = 0; s < kDecWSlots; ++s) {
@@ -220,47 +223,45 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
       uint32_t phase = 0;
       uint32_t issued_mask = 0, last_parity_mask = 0;
       bool alive = true;
-      for (int q = 0; q < 2 && alive; ++q) {
-        if (q == 1 && u_begin[1] < u_end[1]) {
-          // h is complete once every CTA has counted itself in (release/acquire through the counter)
-          const unsigned long long t0 = global_timer_ns();
-          while (ld_acquire_gpu(p.handover) < gridDim.x) {
-            __nanosleep(64);
-            if (wd.aborted()) {
-              alive = false;
-              break;
-            }
-            if (global_timer_ns() - t0 > kWaitLimitNs) {
-              wd.give_up(kSiteDecode);
-              alive = false;
-              break;
-            }
-          }
-          if (!alive) break;
-          // h was written with ordinary stores by other SMs; order them before this SM's TMA reads
-          asm volatile("fence.proxy.async;" ::: "memory");
-          FSW_TRACE(7);
+      auto push = [&](const CUtensorMap* map, int kb) -> bool {
+        if (!wd.wait(x_empty(slot), phase ^ 1u, kSiteProducerEmpty)) return false;
+        mbar_arrive_expect_tx(x_full(slot), x_slot_bytes);
+        tma_load_2d_hint(x_ring + slot * x_slot_bytes, map, x_full(slot), kb * 64, 0, keep);
+        issued_mask |= 1u << slot;
+        last_parity_mask = (last_parity_mask & ~(1u << slot)) | (phase << slot);
+        if (++slot == x_slots) {
+          slot = 0;
+          phase ^= 1u;
         }
-        const CUtensorMap* map = (q == 0) ? &map_x : &map_h;
-        const int kbs = p.ph[q].k_blocks;
-        for (long long u = u_begin[q]; u < u_end[q]; ++u) {
-          const int kb = static_cast<int>(u % kbs);
-          if (!wd.wait(x_empty(slot), phase ^ 1u, kSiteProducerEmpty)) {
+        return true;
+      };
+      for (int i = 0; i < p.tiles_per_cta && alive; ++i) {
+        if (tile_row0(i) >= p.F) break;
+        for (int kb = 0; kb < p.k_blocks1 && alive; ++kb) alive = push(&map_x, kb);
+      }
+      if (alive && u_begin < u_end) {
+        // h is complete once every CTA has counted itself in (release/acquire through the counter)
+        const unsigned long long t0 = global_timer_ns();
+        while (ld_acquire_gpu(p.handover) < gridDim.x) {
+          __nanosleep(32);
+          if (wd.aborted()) {
             alive = false;
             break;
           }
-          mbar_arrive_expect_tx(x_full(slot), x_tile_tx);
-          tma_load_2d_hint(x_ring + slot * kDecXTileBytes, map, x_full(slot), kb * 64, 0, keep);
-          issued_mask |= 1u << slot;
-          last_parity_mask = (last_parity_mask & ~(1u << slot)) | (phase << slot);
-          if (++slot == kDecXSlots) {
-            slot = 0;
-            phase ^= 1u;
+          if (global_timer_ns() - t0 > kWaitLimitNs) {
+            wd.give_up(kSiteDecode);
+            alive = false;
+            break;
           }
         }
+        // h was written with ordinary stores by other SMs; order them before this SM's TMA reads
+        asm volatile("fence.proxy.async;" ::: "memory");
+      }
+      for (long long u = u_begin; u < u_end && alive; ++u) {
+        alive = push(&map_h, static_cast<int>(u % p.k_blocks2));
       }
       if (wd.aborted()) {
-        for (int s = 0; s < kDecXSlots; ++s) {
+        for (int s = 0; s < x_slots; ++s) {
           if (issued_mask & (1u << s)) {
             const uint32_t par = (last_parity_mask >> s) & 1u;
             const unsigned long long t0 = global_timer_ns();
@@ -283,72 +284,94 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
       int acc = 0;
       uint32_t acc_phase = 0;
       bool alive = true;
-      for (int q = 0; q < 2 && alive; ++q) {
-        const int kbs = p.ph[q].k_blocks;
-        long long u = u_begin[q];
-        while (u < u_end[q] && alive) {
-          const int rb = static_cast<int>(u / kbs);
-          const long long seg_end = min(u_end[q], static_cast<long long>(rb + 1) * kbs);
-          if (!wd.wait(tempty_bar(acc), acc_phase ^ 1u, kSiteMmaTmemEmpty)) {
+      auto next_w = [&]() {
+        if (++ws == kDecWSlots) {
+          ws = 0;
+          wphase ^= 1u;
+        }
+      };
+      auto next_x = [&]() {
+        if (++xs == x_slots) {
+          xs = 0;
+          xphase ^= 1u;
+        }
+      };
+      // ---- phase 1: one accumulator pair (gate | up) per tile, whole K ----
+      for (int i = 0; i < p.tiles_per_cta && alive; ++i) {
+        if (tile_row0(i) >= p.F) break;
+        if (!wd.wait(tempty_bar(acc), acc_phase ^ 1u, kSiteMmaTmemEmpty)) {
+          alive = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kAccStride);
+        for (int kb = 0; kb < p.k_blocks1; ++kb) {
+          const int w0 = ws;
+          if (!wd.wait(w_full(w0), wphase, kSiteMmaFull)) {
+            alive = false;
+            break;
+          }
+          next_w();
+          const int w1 = ws;
+          if (!wd.wait(w_full(w1), wphase, kSiteMmaFull) || !wd.wait(x_full(xs), xphase, kSiteMmaFull)) {
+            alive = false;
+            break;
+          }
+          next_w();
+          tc_fence_after_sync();
+          const uint64_t g_desc = umma_desc_k_sw128(w_ring + w0 * kDecWSlotBytes);
+          const uint64_t u_desc = umma_desc_k_sw128(w_ring + w1 * kDecWSlotBytes);
+          const uint64_t x_desc = umma_desc_k_sw128(x_ring + xs * x_slot_bytes);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
+            umma_bf16_ss(d_tmem, g_desc + 2u * k, x_desc + 2u * k, idesc, accum);
+            umma_bf16_ss(d_tmem + p.n_pad, u_desc + 2u * k, x_desc + 2u * k, idesc, accum);
+          }
+          umma_commit(w_empty(w0));
+          umma_commit(w_empty(w1));
+          umma_commit(x_empty(xs));
+          next_x();
+        }
+        if (!alive) break;
+        umma_commit(tfull_bar(acc));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+      // ---- phase 2: one accumulator per (row-block, k-range) segment ----
+      long long u = u_begin;
+      while (u < u_end && alive) {
+        const int rb = static_cast<int>(u / p.k_blocks2);
+        const long long seg_end = min(u_end, static_cast<long long>(rb + 1) * p.k_blocks2);
+        if (!wd.wait(tempty_bar(acc), acc_phase ^ 1u, kSiteMmaTmemEmpty)) {
+          alive = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kAccStride);
+        bool first = true;
+        for (; u < seg_end; ++u) {
+          if (!wd.wait(w_full(ws), wphase, kSiteMmaFull) || !wd.wait(x_full(xs), xphase, kSiteMmaFull)) {
             alive = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kAccStride);
-          bool first = true;
-          for (; u < seg_end; ++u) {
-            // weight tile(s) of this unit, then its token tile
-            const int w0 = ws;
-            if (!wd.wait(w_full(w0), wphase, kSiteMmaFull)) {
-              alive = false;
-              break;
-            }
-            if (++ws == kDecWSlots) {
-              ws = 0;
-              wphase ^= 1u;
-            }
-            int w1 = w0;
-            if (q == 0) {
-              w1 = ws;
-              if (!wd.wait(w_full(w1), wphase, kSiteMmaFull)) {
-                alive = false;
-                break;
-              }
-              if (++ws == kDecWSlots) {
-                ws = 0;
-                wphase ^= 1u;
-              }
-            }
-            if (!wd.wait(x_full(xs), xphase, kSiteMmaFull)) {
-              alive = false;
-              break;
-            }
-            tc_fence_after_sync();
-            if (first && u == u_begin[q]) FSW_TRACE(q == 0 ? 1 : 4);
-            const uint64_t w0_desc = umma_desc_k_sw128(w_ring + w0 * kDecWTileBytes);
-            const uint64_t w1_desc = umma_desc_k_sw128(w_ring + w1 * kDecWTileBytes);
-            const uint64_t x_desc = umma_desc_k_sw128(x_ring + xs * kDecXTileBytes);
+          const uint64_t w_desc = umma_desc_k_sw128(w_ring + ws * kDecWSlotBytes);
+          const uint64_t x_desc = umma_desc_k_sw128(x_ring + xs * x_slot_bytes);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const uint32_t accum = (first && k == 0) ? 0u : 1u;
-              umma_bf16_ss(d_tmem, w0_desc + 2u * k, x_desc + 2u * k, idesc, accum);
-              if (q == 0) umma_bf16_ss(d_tmem + p.n_pad, w1_desc + 2u * k, x_desc + 2u * k, idesc, accum);
-            }
-            first = false;
-            umma_commit(w_empty(w0));
-            if (q == 0) umma_commit(w_empty(w1));
-            umma_commit(x_empty(xs));
-            if (++xs == kDecXSlots) {
-              xs = 0;
-              xphase ^= 1u;
-            }
+          for (int k = 0; k < 4; ++k) {
+            umma_bf16_ss(d_tmem, w_desc + 2u * k, x_desc + 2u * k, idesc, (first && k == 0) ? 0u : 1u);
           }
-          if (!alive) break;
-          umma_commit(tfull_bar(acc));
-          acc ^= 1;
-          if (acc == 0) acc_phase ^= 1u;
+          first = false;
+          umma_commit(w_empty(ws));
+          umma_commit(x_empty(xs));
+          next_w();
+          next_x();
         }
-        FSW_TRACE(q == 0 ? 2 : 5);
+        if (!alive) break;
+        umma_commit(tfull_bar(acc));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
       }
       if (wd.aborted()) {
         umma_commit(drain_bar);
@@ -364,141 +387,155 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
   } else {
     // -------------------------------------- epilogue -------------------------------------------
     const int quarter = warp & 3;
-    const int row_in_block = quarter * 32 + static_cast<int>(lane);  // weight row within the row-block
+    const int row_in_tile = quarter * 32 + static_cast<int>(lane);  // weight row within the tile / row-block
     const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
     const int epi_tid = static_cast<int>(threadIdx.x) - 64;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool alive = true;
-    uint32_t seg_iter = 0;
-    for (int q = 0; q < 2 && alive; ++q) {
-      const DecodePhase& ph = p.ph[q];
-      const bool gated = (q == 0);
-      const int acc_cols = gated ? 2 * p.n_pad : p.n_pad;
-      long long u = u_begin[q];
-      while (u < u_end[q]) {
-        const int rb = static_cast<int>(u / ph.k_blocks);
-        const long long rb_first = static_cast<long long>(rb) * ph.k_blocks;
-        const long long seg_end = min(u_end[q], rb_first + ph.k_blocks);
-        // which contiguous ranges (CTAs) share this row-block, and which of them am I
-        const int first_cta = dec_owner(rb_first, units[q], gridDim.x);
-        const int last_cta = dec_owner(rb_first + ph.k_blocks - 1, units[q], gridDim.x);
-        const int nseg = last_cta - first_cta + 1;
-        const int seg = static_cast<int>(blockIdx.x) - first_cta;
-        u = seg_end;
+    uint32_t iter = 0;
+    // One thread waits for the accumulator and tells the other 127: the four epilogue warps share
+    // named barriers below, so they must all take the same exit if a wait gives up.
+    auto accumulator_ready = [&]() -> bool {
+      if (epi_tid == 0) epi_ok[iter & 1u] = wd.wait(tfull_bar(acc), acc_phase, kSiteEpilogueFull) ? 1u : 0u;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const uint32_t ok = epi_ok[iter & 1u];
+      ++iter;
+      return ok != 0;
+    };
+    auto release_accumulator = [&]() {
+      tc_fence_before_sync();
+      mbar_arrive(tempty_bar(acc));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    };
 
-        // One thread waits for the accumulator and tells the other 127: the four epilogue warps
-        // share named barriers below, so they must all take the same exit if a wait gives up.
-        if (epi_tid == 0) epi_ok[seg_iter & 1u] = wd.wait(tfull_bar(acc), acc_phase, kSiteEpilogueFull) ? 1u : 0u;
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        const uint32_t ok = epi_ok[seg_iter & 1u];
-        ++seg_iter;
-        if (!ok) {
-          alive = false;
-          break;
-        }
-        tc_fence_after_sync();
-        const uint32_t t_acc = tmem_base + lane_field + static_cast<uint32_t>(acc * kAccStride);
-        const int out_row = rb * 128 + row_in_block;  // output feature index
-
-        bool reduce_here = true;
-        if (nseg > 1) {
-          // publish this segment's partial sums: [row][acc_cols] fp32, one contiguous run per thread
-          float* my_tile =
-              ph.partials + ((static_cast<size_t>(rb) * kDecMaxSegments + seg) * 128 + row_in_block) * acc_cols;
+    // ---- phase 1: h = silu(g) * u straight from the accumulators ----
+    for (int i = 0; i < p.tiles_per_cta; ++i) {
+      const long long row0 = tile_row0(i);
+      if (row0 >= p.F) break;
+      if (!accumulator_ready()) {
+        alive = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t t_acc = tmem_base + lane_field + static_cast<uint32_t>(acc * kAccStride);
+      const long long j = row0 + row_in_tile;  // hidden unit
+      const bool row_ok = row_in_tile < p.tile_rows && j < p.F;
+      __nv_bfloat16* h = reinterpret_cast<__nv_bfloat16*>(p.h);
 #pragma unroll 1
-          for (int c0 = 0; c0 < acc_cols; c0 += 16) {
+      for (int c0 = 0; c0 < p.n_pad; c0 += 16) {
+        uint32_t g[16], uu[16];
+        tmem_ld_32x32b_x16(t_acc + c0, g);
+        tmem_ld_32x32b_x16(t_acc + p.n_pad + c0, uu);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int t = 0; t < 16; ++t) {
+            if (c0 + t < p.M) {
+              h[static_cast<long long>(c0 + t) * p.F + j] =
+                  __float2bfloat16_rn(silu_mul(__uint_as_float(g[t]), __uint_as_float(uu[t])));
+            }
+          }
+        }
+      }
+      release_accumulator();
+    }
+    // hand-over: everything this CTA contributes to h is written; count it in
+    __threadfence();
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (epi_tid == 0 && alive) {
+      asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.handover) : "memory");
+    }
+
+    // ---- phase 2: segments of row-blocks, combined through fp32 partial tiles ----
+    long long u = u_begin;
+    while (u < u_end && alive) {
+      const int rb = static_cast<int>(u / p.k_blocks2);
+      const long long rb_first = static_cast<long long>(rb) * p.k_blocks2;
+      const long long seg_end = min(u_end, rb_first + p.k_blocks2);
+      // which contiguous ranges (CTAs) share this row-block, and which of them am I
+      const int first_cta = dec_owner(rb_first, units2, gridDim.x);
+      const int last_cta = dec_owner(rb_first + p.k_blocks2 - 1, units2, gridDim.x);
+      const int nseg = last_cta - first_cta + 1;
+      const int seg = static_cast<int>(blockIdx.x) - first_cta;
+      u = seg_end;
+      if (!accumulator_ready()) {
+        alive = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t t_acc = tmem_base + lane_field + static_cast<uint32_t>(acc * kAccStride);
+      const long long out_row = static_cast<long long>(rb) * 128 + row_in_tile;
+
+      bool reduce_here = true;
+      if (nseg > 1) {
+        // publish this segment's partial sums: [row][n_pad] fp32, one contiguous run per thread
+        float* my_tile =
+            p.partials + ((static_cast<size_t>(rb) * kDecMaxSegments + seg) * 128 + row_in_tile) * p.n_pad;
+#pragma unroll 1
+        for (int c0 = 0; c0 < p.n_pad; c0 += 16) {
+          uint32_t r[16];
+          tmem_ld_32x32b_x16(t_acc + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            __stcg(reinterpret_cast<float4*>(my_tile + c0) + i,
+                   make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                               __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3])));
+          }
+        }
+        release_accumulator();  // accumulator drained: the MMA warp may reuse it
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (epi_tid == 0) {
+          const unsigned int old = atomicAdd(p.counters + rb, 1u);
+          *last_flag = (old == static_cast<unsigned int>(nseg - 1)) ? 1u : 0u;
+          __threadfence();
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        reduce_here = (*last_flag != 0);
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // everyone has read the flag before it is reused
+      }
+      if (reduce_here) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < p.n_pad; c0 += 16) {
+          float a[16];
+          if (nseg > 1) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) a[i] = 0.0f;
+            for (int s = 0; s < nseg; ++s) {  // fixed order: the result does not depend on arrival order
+              const float* tile =
+                  p.partials + ((static_cast<size_t>(rb) * kDecMaxSegments + s) * 128 + row_in_tile) * p.n_pad;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(tile + c0) + i);
+                a[4 * i] += v.x; a[4 * i + 1] += v.y; a[4 * i + 2] += v.z; a[4 * i + 3] += v.w;
+              }
+            }
+          } else {
             uint32_t r[16];
             tmem_ld_32x32b_x16(t_acc + c0, r);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              __stcg(reinterpret_cast<float4*>(my_tile + c0) + i,
-                     make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
-                                 __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3])));
-            }
+            for (int i = 0; i < 16; ++i) a[i] = __uint_as_float(r[i]);
           }
-          tc_fence_before_sync();
-          mbar_arrive(tempty_bar(acc));  // accumulator drained: the MMA warp may reuse it
-          __threadfence();
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (epi_tid == 0) {
-            const unsigned int old = atomicAdd(ph.counters + rb, 1u);
-            *last_flag = (old == static_cast<unsigned int>(nseg - 1)) ? 1u : 0u;
-            __threadfence();
-          }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          reduce_here = (*last_flag != 0);
-          asm volatile("bar.sync 1, 128;" ::: "memory");  // everyone has read the flag before it is reused
-        }
-
-        if (reduce_here) {
-          // complete sums for this thread's weight row, 16 token columns at a time
-#pragma unroll 1
-          for (int c0 = 0; c0 < p.n_pad; c0 += 16) {
-            float a[16], b[16];
-            if (nseg > 1) {
+          if (out_row < p.d) {
 #pragma unroll
-              for (int i = 0; i < 16; ++i) a[i] = b[i] = 0.0f;
-              for (int s = 0; s < nseg; ++s) {  // fixed order: the result does not depend on arrival order
-                const float* tile =
-                    ph.partials + ((static_cast<size_t>(rb) * kDecMaxSegments + s) * 128 + row_in_block) * acc_cols;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  const float4 v = __ldcg(reinterpret_cast<const float4*>(tile + c0) + i);
-                  a[4 * i] += v.x; a[4 * i + 1] += v.y; a[4 * i + 2] += v.z; a[4 * i + 3] += v.w;
-                  if (gated) {
-                    const float4 w = __ldcg(reinterpret_cast<const float4*>(tile + p.n_pad + c0) + i);
-                    b[4 * i] += w.x; b[4 * i + 1] += w.y; b[4 * i + 2] += w.z; b[4 * i + 3] += w.w;
-                  }
-                }
-              }
-            } else {
-              uint32_t r[16], s2[16];
-              tmem_ld_32x32b_x16(t_acc + c0, r);
-              if (gated) tmem_ld_32x32b_x16(t_acc + p.n_pad + c0, s2);
-              tmem_ld_wait();
-#pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                a[i] = __uint_as_float(r[i]);
-                b[i] = gated ? __uint_as_float(s2[i]) : 0.0f;
-              }
-            }
-            if (out_row < ph.n_rows) {
-#pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                const int t = c0 + i;  // token
-                if (t < p.M) {
-                  const float v = gated ? silu_mul(a[i], b[i]) : a[i];
-                  const long long off = static_cast<long long>(t) * ph.ld_out + out_row;
-                  if (!gated && ph.out_f32) {
-                    reinterpret_cast<float*>(ph.out)[off] = v;
-                  } else {
-                    reinterpret_cast<__nv_bfloat16*>(ph.out)[off] = __float2bfloat16_rn(v);
-                  }
+            for (int t = 0; t < 16; ++t) {
+              if (c0 + t < p.M) {
+                const long long off = static_cast<long long>(c0 + t) * p.ld_out + out_row;
+                if (p.out_f32) {
+                  reinterpret_cast<float*>(p.out)[off] = a[t];
+                } else {
+                  reinterpret_cast<__nv_bfloat16*>(p.out)[off] = __float2bfloat16_rn(a[t]);
                 }
               }
             }
           }
         }
-        if (nseg == 1) {
-          tc_fence_before_sync();
-          mbar_arrive(tempty_bar(acc));
-        }
-        acc ^= 1;
-        if (acc == 0) acc_phase ^= 1u;
       }
-      if (q == 0) {
-        // hand-over: everything this CTA contributes to h is written; count it in
-        __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (epi_tid == 0 && alive) {
-          asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.handover) : "memory");
-          FSW_TRACE(3);
-        }
-      } else if (epi_tid == 0) {
-        FSW_TRACE(6);
-      }
+      if (nseg == 1) release_accumulator();
     }
   }
 
@@ -522,21 +559,28 @@ inline int decode_pad_tokens(int64_t M) { return M <= 16 ? 16 : (M <= 32 ? 32 : 
 
 inline size_t decode_round256(size_t v) { return (v + 255) / 256 * 256; }
 
-// hand-over counter + arrival counters (both phases) | phase-1 partial tiles | phase-2 partial tiles
-inline size_t decode_counter_bytes(int64_t d, int64_t F) {
-  const size_t rb1 = static_cast<size_t>((F + 127) / 128), rb2 = static_cast<size_t>((d + 127) / 128);
-  return decode_round256((1 + rb1 + rb2) * sizeof(unsigned int));
+// hand-over counter + per-row-block arrival counters | phase-2 partial tiles
+inline size_t decode_counter_bytes(int64_t d) {
+  return decode_round256((1 + static_cast<size_t>((d + 127) / 128)) * sizeof(unsigned int));
 }
-inline size_t decode_workspace_bytes(int64_t M, int64_t d, int64_t F) {
+inline size_t decode_workspace_bytes(int64_t M, int64_t d, int64_t) {
   const size_t n = static_cast<size_t>(decode_pad_tokens(M));
-  const size_t rb1 = static_cast<size_t>((F + 127) / 128), rb2 = static_cast<size_t>((d + 127) / 128);
-  size_t bytes = decode_counter_bytes(d, F);
-  bytes += decode_round256(rb1 * kDecMaxSegments * 128 * (2 * n) * sizeof(float));
-  bytes += decode_round256(rb2 * kDecMaxSegments * 128 * n * sizeof(float));
-  return bytes;
+  const size_t rb2 = static_cast<size_t>((d + 127) / 128);
+  return decode_counter_bytes(d) + decode_round256(rb2 * kDecMaxSegments * 128 * n * sizeof(float));
 }
 
-// Largest grid (<= SM count) that keeps every row-block of a phase within kDecMaxSegments ranges.
+// Phase 1: even row split over `num_sms` CTAs, rows per CTA cut into tiles of <= 128 rows.
+inline void decode_plan_rows(int64_t n_rows, int num_sms, int* tile_rows, int* tiles_per_cta, int* ctas_used) {
+  int64_t per = (n_rows + num_sms - 1) / num_sms;
+  if (per < 8) per = n_rows < 8 ? n_rows : 8;
+  const int64_t tiles = (per + 127) / 128;
+  const int64_t rows = (per + tiles - 1) / tiles;
+  *tile_rows = static_cast<int>(rows);
+  *tiles_per_cta = static_cast<int>(tiles);
+  *ctas_used = static_cast<int>((n_rows + rows * tiles - 1) / (rows * tiles));
+}
+
+// Phase 2: largest grid (<= SM count) that keeps every row-block within kDecMaxSegments ranges.
 inline int decode_grid_limit(int64_t row_blocks, int64_t k_blocks, int num_sms) {
   const int64_t units = row_blocks * k_blocks;
   int64_t g = units < num_sms ? units : num_sms;
