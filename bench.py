@@ -190,6 +190,8 @@ def run_ours(args, rank, local_rank, world):
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     if world > 1:
+        # the collectives run beside persistent GEMMs: cap NCCL's CTAs to the SMs the GEMMs leave free
+        os.environ.setdefault("NCCL_MAX_CTAS", str(args.comm_sms))
         dist.init_process_group("nccl", device_id=dev)
     name = args.workload or ("c2_llama2_7b_prefill" if world == 1 else "c4_llama3_70b_prefill")
     cfg = WORKLOADS[name]
@@ -242,13 +244,26 @@ def run_ours(args, rank, local_rank, world):
             rc |= lib.fswiglu_down_bf16(vp(hbuf), Fl, vp(dn_), Fl, vp(out_f32), d, rows, d, Fl, capi.OUT_F32, sp)
             capi.check(rc, "bench tp step")
 
-        tp = TensorParallelSwiGLU(wg, wu, wd, n_slabs=args.slabs, mode=args.tp_mode, local_partial=local_partial)
+        tp = TensorParallelSwiGLU(wg, wu, wd, n_slabs=args.slabs, mode=args.tp_mode, local_partial=local_partial,
+                                  comm_sms=args.comm_sms)
         gateup_rows = max(r1 - r0 for r0, r1 in tp.slab_bounds(M))
+        pending = []
+
+        def trace(tag):
+            if not record_flag["on"]:
+                return
+            e = torch.cuda.Event(enable_timing=True)
+            e.record(stream)
+            if tag == "gateup_begin":
+                pending.append(e)
+            else:
+                gateup_events.append((pending.pop(), e))
+        tp.trace = trace
 
         def step(record):
             record_flag["on"] = record
             return tp.forward(x)
-        parallelism = f"tp{world} (Megatron: gate/up column-split, down row-split, fp32 {args.tp_mode}, " \
+        parallelism = f"tp{world} (Megatron: gate/up column-split, down row-split, {args.tp_mode}, " \
                       f"{args.slabs} row slabs overlapped)"
 
     def barrier():
@@ -368,7 +383,8 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default=None)
     ap.add_argument("--e2e-steps", type=int, default=50)
     ap.add_argument("--slabs", type=int, default=4)
-    ap.add_argument("--tp-mode", choices=["allreduce", "rs_ag"], default="allreduce")
+    ap.add_argument("--tp-mode", choices=["allreduce", "rs_ag", "push"], default="push")
+    ap.add_argument("--comm-sms", type=int, default=16, help="SMs left to the collective kernels when N > 1")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))

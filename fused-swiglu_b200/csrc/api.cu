@@ -40,6 +40,51 @@ __global__ void __launch_bounds__(256) cast_f32_to_bf16_kernel(const float4* __r
   }
 }
 
+// Second half of the tensor-parallel reduction: this rank owns `rows` rows; recv holds one bf16
+// partial copy of them per source rank ([world][rows][cols], local memory, written by the ranks'
+// down-GEMM epilogues).  Sum the copies in fp32 in rank order (every element is reduced by exactly one
+// rank, so all ranks end up with identical bits), round once, and store the result into every
+// rank's output buffer (peer stores over NVLink).  16 bytes per thread per step.
+struct ReduceBcastParams {
+  const uint4* recv;
+  void* out[8];          // per destination rank: base of its [*, cols] output, already offset to these rows
+  long long n16;         // rows * cols / 8
+  int world;
+};
+__global__ void __launch_bounds__(256) reduce_bcast_bf16_kernel(const ReduceBcastParams p) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < p.n16; i += stride) {
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.0f;
+    uint4 v[8];
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+      if (s < p.world) v[s] = __ldcs(p.recv + s * p.n16 + i);
+    }
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+      if (s < p.world) {
+        const uint32_t w[4] = {v[s].x, v[s].y, v[s].z, v[s].w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          acc[2 * k] += __uint_as_float(w[k] << 16);
+          acc[2 * k + 1] += __uint_as_float(w[k] & 0xffff0000u);
+        }
+      }
+    }
+    uint4 q;
+    q.x = pack_bf16x2(acc[0], acc[1]);
+    q.y = pack_bf16x2(acc[2], acc[3]);
+    q.z = pack_bf16x2(acc[4], acc[5]);
+    q.w = pack_bf16x2(acc[6], acc[7]);
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+      if (s < p.world) reinterpret_cast<uint4*>(p.out[s])[i] = q;
+    }
+  }
+}
+
 }  // namespace fsw
 
 namespace {
@@ -66,6 +111,7 @@ struct DeviceState {
 std::mutex g_mutex;
 DeviceState g_dev[kMaxDevices];
 std::atomic<uint64_t> g_launches{0};
+std::atomic<int> g_max_ctas{0};  // 0 = use every SM
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                    const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -189,11 +235,19 @@ int pick_tile_n(int num_m_tiles, int64_t n_out, int max_tile, int mma_per_col, i
   return best < needed ? best : (needed < 16 ? 16 : needed);
 }
 
+int effective_ctas(const DeviceState& st) {
+  const int cap = g_max_ctas.load(std::memory_order_relaxed);
+  return (cap > 0 && cap < st.num_sms) ? cap : st.num_sms;
+}
+
 template <int kMode, bool kOutF32>
 int launch_gemm(const DeviceState& st, const CUtensorMap& ma, const CUtensorMap& mb0,
                 const CUtensorMap& mb1, const GemmParams& p, cudaStream_t stream) {
   const int tiles = p.num_m_tiles * p.num_n_tiles;
-  const int grid = tiles < st.num_sms ? tiles : st.num_sms;
+  int ctas = st.num_sms;
+  const int cap = g_max_ctas.load(std::memory_order_relaxed);
+  if (cap > 0 && cap < ctas) ctas = cap;
+  const int grid = tiles < ctas ? tiles : ctas;
   gemm_tcgen05_kernel<kMode, kOutF32><<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(ma, mb0, mb1, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError() == cudaSuccess ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
@@ -214,14 +268,14 @@ int gateup_impl(DeviceState& st, const void* x, int64_t ldx, const void* w0, int
   }
   if ((rc = check_matrix(h, M, F, ldh, false))) return rc;
 
-  GemmParams p;
+  GemmParams p = {};
   p.out = h;
   p.ld_out = ldh;
   p.M = static_cast<int>(M);
   p.n_out = static_cast<int>(F);
   p.K = static_cast<int>(d);
   p.num_m_tiles = static_cast<int>((M + 127) / 128);
-  p.tile_n = pick_tile_n(p.num_m_tiles, F, 128, 2, st.num_sms);
+  p.tile_n = pick_tile_n(p.num_m_tiles, F, 128, 2, effective_ctas(st));
   p.num_n_tiles = static_cast<int>((F + p.tile_n - 1) / p.tile_n);
   CUtensorMap ma, mb0, mb1;
   if ((rc = encode_map(&ma, x, M, d, ldx, 128))) return rc;
@@ -248,14 +302,14 @@ int down_impl(DeviceState& st, const void* h, int64_t ldh, const void* w_down, i
   if ((rc = check_matrix(w_down, d, F, ldw, true))) return rc;
   if ((rc = check_matrix(out, M, d, ldo, false))) return rc;
 
-  GemmParams p;
+  GemmParams p = {};
   p.out = out;
   p.ld_out = ldo;
   p.M = static_cast<int>(M);
   p.n_out = static_cast<int>(d);
   p.K = static_cast<int>(F);
   p.num_m_tiles = static_cast<int>((M + 127) / 128);
-  p.tile_n = pick_tile_n(p.num_m_tiles, d, 256, 1, st.num_sms);
+  p.tile_n = pick_tile_n(p.num_m_tiles, d, 256, 1, effective_ctas(st));
   p.num_n_tiles = static_cast<int>((d + p.tile_n - 1) / p.tile_n);
   CUtensorMap ma, mb;
   if ((rc = encode_map(&ma, h, M, F, ldh, 128))) return rc;
@@ -573,6 +627,74 @@ int fswiglu_cast_f32_to_bf16(const void* src, void* dst, int64_t n, void* stream
       static_cast<__nv_bfloat16*>(dst) + n8 * 8, tail);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError() == cudaSuccess ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
+}
+
+int fswiglu_down_scatter_bf16(const void* h, int64_t ldh, const void* w_down, int64_t ldw,
+                              void* const* recv_ptrs, int world, int rank, int64_t rows_per_owner, int64_t M,
+                              int64_t d, int64_t F, void* stream) {
+  if (M < 0 || F <= 0 || d <= 0 || world < 1 || world > 8 || rank < 0 || rank >= world || rows_per_owner <= 0 ||
+      recv_ptrs == nullptr)
+    return FSWIGLU_ERR_BAD_ARG;
+  if (M > rows_per_owner * world) return FSWIGLU_ERR_SHAPE;
+  if (M == 0) return FSWIGLU_OK;
+  if (d % 8 != 0) return FSWIGLU_ERR_SHAPE;
+  DeviceState* st = nullptr;
+  if (int rc = device_state(&st)) return rc;
+  int rc;
+  if ((rc = check_matrix(h, M, F, ldh, true))) return rc;
+  if ((rc = check_matrix(w_down, d, F, ldw, true))) return rc;
+  GemmParams p = {};
+  for (int r = 0; r < world; ++r) {
+    if (recv_ptrs[r] == nullptr || !aligned16(recv_ptrs[r])) return FSWIGLU_ERR_ALIGNMENT;
+    p.peer_out[r] = recv_ptrs[r];
+  }
+  p.out = nullptr;
+  p.ld_out = d;
+  p.M = static_cast<int>(M);
+  p.n_out = static_cast<int>(d);
+  p.K = static_cast<int>(F);
+  p.num_m_tiles = static_cast<int>((M + 127) / 128);
+  p.tile_n = pick_tile_n(p.num_m_tiles, d, 256, 1, effective_ctas(*st));
+  p.num_n_tiles = static_cast<int>((d + p.tile_n - 1) / p.tile_n);
+  p.group_m = pick_group_m(p.num_m_tiles, F);
+  p.vec_ok = 1;
+  p.status = st->status;
+  p.scatter_world = world;
+  p.scatter_rank = rank;
+  p.rows_per_owner = static_cast<int>(rows_per_owner);
+  CUtensorMap ma, mb;
+  if ((rc = encode_map(&ma, h, M, F, ldh, 128))) return rc;
+  if ((rc = encode_map(&mb, w_down, d, F, ldw, p.tile_n))) return rc;
+  return launch_gemm<kPlain, false>(*st, ma, mb, mb, p, static_cast<cudaStream_t>(stream));
+}
+
+int fswiglu_reduce_bcast_bf16(const void* recv_local, void* const* out_ptrs, int world, int64_t rows, int64_t cols,
+                              int max_ctas, void* stream) {
+  if (world < 1 || world > 8 || rows < 0 || cols <= 0 || out_ptrs == nullptr) return FSWIGLU_ERR_BAD_ARG;
+  if (rows == 0) return FSWIGLU_OK;
+  if (recv_local == nullptr) return FSWIGLU_ERR_BAD_ARG;
+  if ((rows * cols) % 8 != 0) return FSWIGLU_ERR_SHAPE;
+  if (!aligned16(recv_local)) return FSWIGLU_ERR_ALIGNMENT;
+  DeviceState* st = nullptr;
+  if (int rc = device_state(&st)) return rc;
+  ReduceBcastParams p = {};
+  p.recv = static_cast<const uint4*>(recv_local);
+  for (int r = 0; r < world; ++r) {
+    if (out_ptrs[r] == nullptr || !aligned16(out_ptrs[r])) return FSWIGLU_ERR_ALIGNMENT;
+    p.out[r] = out_ptrs[r];
+  }
+  p.n16 = rows * cols / 8;
+  p.world = world;
+  int ctas = max_ctas > 0 ? max_ctas : 32;
+  const long long need = (p.n16 + 255) / 256;
+  if (ctas > need) ctas = static_cast<int>(need);
+  reduce_bcast_bf16_kernel<<<ctas, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
+}
+
+int fswiglu_set_max_ctas(int max_ctas) {
+  return g_max_ctas.exchange(max_ctas < 0 ? 0 : max_ctas, std::memory_order_relaxed);
 }
 
 int fswiglu_device_status(uint32_t* status, void* stream) {

@@ -66,7 +66,27 @@ struct GemmParams {
   int group_m;        // rasterisation: this many M-tiles share a sweep over N
   int vec_ok;         // 1 when every row start of `out` is 16-byte aligned
   uint32_t* status;   // device watchdog word (0 = healthy)
+  // Tensor-parallel reduce-scatter by direct stores (plain mode, bf16 out): when scatter_world > 0
+  // output row r belongs to rank r / rows_per_owner and is written straight into that rank's
+  // receive buffer peer_out[owner] (peer memory over NVLink, or local memory for the own rank),
+  // at row  scatter_rank * rows_per_owner + (r mod rows_per_owner)  of a [world * rows_per_owner,
+  // n_out] matrix with row pitch ld_out.  `out` is unused then.
+  int scatter_world;
+  int scatter_rank;
+  int rows_per_owner;
+  void* peer_out[8];
 };
+
+// Where output row `row` lives: (base pointer, row index inside that base).
+__device__ __forceinline__ void* out_row_base(const GemmParams& p, int row, long long* local_row) {
+  if (p.scatter_world > 0) {
+    const int owner = row / p.rows_per_owner;
+    *local_row = static_cast<long long>(p.scatter_rank) * p.rows_per_owner + (row - owner * p.rows_per_owner);
+    return p.peer_out[owner];
+  }
+  *local_row = row;
+  return p.out;
+}
 
 struct TileCoord {
   int m_tile;
@@ -94,8 +114,10 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, int row, int co
   // v holds `ncols` (16 or 32) consecutive output columns of one row, starting at col0.
   if (row >= p.M || col0 >= p.n_out) return;
   const int valid = min(ncols, p.n_out - col0);
+  long long lrow;
+  void* base = out_row_base(p, row, &lrow);
   if constexpr (kOutF32) {
-    float* dst = reinterpret_cast<float*>(p.out) + static_cast<long long>(row) * p.ld_out + col0;
+    float* dst = reinterpret_cast<float*>(base) + lrow * p.ld_out + col0;
     if (p.vec_ok && valid == ncols) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -109,8 +131,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, int row, int co
       }
     }
   } else {
-    __nv_bfloat16* dst =
-        reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(row) * p.ld_out + col0;
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(base) + lrow * p.ld_out + col0;
     if (p.vec_ok && valid == ncols) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {

@@ -37,6 +37,10 @@ SIGNATURES = {
     "fswiglu_host_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "fswiglu_mlp_bf16_static": (_int, [_vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _int, _i64, _i64, _i64, _vp]),
     "fswiglu_cast_f32_to_bf16": (_int, [_vp, _vp, _i64, _vp]),
+    "fswiglu_down_scatter_bf16": (_int, [_vp, _i64, _vp, _i64, ctypes.POINTER(ctypes.c_void_p), _int, _int, _i64, _i64,
+                                         _i64, _i64, _vp]),
+    "fswiglu_reduce_bcast_bf16": (_int, [_vp, ctypes.POINTER(ctypes.c_void_p), _int, _i64, _i64, _int, _vp]),
+    "fswiglu_set_max_ctas": (_int, [_int]),
     "fswiglu_device_status": (_int, [ctypes.POINTER(ctypes.c_uint32), _vp]),
     "fswiglu_status_string": (ctypes.c_char_p, [_int]),
     "fswiglu_version": (ctypes.c_char_p, []),

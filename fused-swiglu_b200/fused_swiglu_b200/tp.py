@@ -29,10 +29,11 @@ import torch.distributed as dist
 from . import pack
 
 
-def _cuda_local_partial(x, w_gate, w_up, w_down, out_f32, workspace):
+def _cuda_local_partial(x, w_gate, w_up, w_down, out_partial, workspace):
     from . import ops
 
-    ops.fused_swiglu_mlp_bf16(x, w_gate, w_up, w_down, out_dtype=torch.float32, workspace=workspace, out=out_f32)
+    ops.fused_swiglu_mlp_bf16(x, w_gate, w_up, w_down, out_dtype=out_partial.dtype, workspace=workspace,
+                              out=out_partial)
 
 
 def _cuda_round(src_f32, dst_bf16):
@@ -53,13 +54,22 @@ class TensorParallelSwiGLU:
     mode "allreduce": fp32 all-reduce of each slab, then one rounding to bf16.
     mode "rs_ag":     fp32 reduce-scatter over rows, rounding of the local rows, bf16 all-gather
                       (a quarter less wire traffic than the fp32 all-reduce).
+    mode "push":      no NCCL on the data path.  The down-GEMM epilogue stores each bf16 partial row
+                      straight into its owner rank's receive buffer (peer memory over NVLink, tile by
+                      tile while the GEMM runs); after a cross-rank barrier every rank sums the copies
+                      of its rows in fp32, rounds once and stores the result into all ranks' outputs.
+                      bf16 on the wire, fp32 accumulation, one rounding; buffers are symmetric memory.
     """
 
     def __init__(self, w_gate_shard: torch.Tensor, w_up_shard: torch.Tensor, w_down_shard: torch.Tensor,
                  group: Optional[dist.ProcessGroup] = None, n_slabs: int = 4, mode: str = "allreduce",
-                 local_partial: Callable = _cuda_local_partial, round_fn: Callable = _cuda_round):
-        if mode not in ("allreduce", "rs_ag"):
-            raise ValueError("mode must be 'allreduce' or 'rs_ag'")
+                 local_partial: Callable = _cuda_local_partial, round_fn: Callable = _cuda_round,
+                 comm_sms: int = 16, wire_dtype: torch.dtype = torch.float32):
+        if mode not in ("allreduce", "rs_ag", "push"):
+            raise ValueError("mode must be 'allreduce', 'rs_ag' or 'push'")
+        if wire_dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError("wire_dtype must be float32 or bfloat16")
+        self.wire_dtype = wire_dtype
         self.w_gate, self.w_up, self.w_down = w_gate_shard, w_up_shard, w_down_shard
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -72,7 +82,16 @@ class TensorParallelSwiGLU:
         self.F_local, self.d = w_gate_shard.shape
         self._bufs = {}
         self._cuda = self.device.type == "cuda"
-        self._comm_stream = torch.cuda.Stream(device=self.device) if self._cuda else None
+        self._comm_stream = torch.cuda.Stream(device=self.device, priority=-1) if self._cuda else None
+        self._reduce_ctas = max(8, comm_sms)
+        self.trace = None  # optional callable(tag): "gateup_begin" / "gateup_end" around that launch (push mode)
+        if self._cuda and self.world > 1 and comm_sms > 0:
+            # leave `comm_sms` SMs to the collective kernels that run beside the GEMMs (the launcher
+            # should cap NCCL to the same number, e.g. NCCL_MAX_CTAS), see fswiglu_set_max_ctas
+            from . import capi
+
+            sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+            capi.lib.fswiglu_set_max_ctas(max(1, sms - comm_sms))
 
     @classmethod
     def from_full(cls, w_gate, w_up, w_down, device, group=None, **kw):
@@ -85,7 +104,7 @@ class TensorParallelSwiGLU:
     # slab r0:r1 boundaries; with rs_ag every slab must split evenly over the ranks
     def slab_bounds(self, M: int):
         n = min(self.n_slabs, max(1, M))
-        quantum = self.world * 8 if self.mode == "rs_ag" else 1
+        quantum = self.world * 8 if self.mode in ("rs_ag", "push") else 1
         per = (M + n - 1) // n
         per = (per + quantum - 1) // quantum * quantum
         bounds = []
@@ -101,11 +120,20 @@ class TensorParallelSwiGLU:
         if key not in self._bufs:
             dev = self.device
             Mp = M
-            if self.mode == "rs_ag":
+            if self.mode in ("rs_ag", "push"):
                 q = self.world
                 Mp = sum(((r1 - r0 + q - 1) // q * q) for r0, r1 in self.slab_bounds(M))
-            partial = torch.empty((Mp, self.d), dtype=torch.float32, device=dev)
-            out = torch.empty((Mp, self.d), dtype=torch.bfloat16, device=dev)
+            if self.mode == "push" and self.world > 1:
+                import torch.distributed._symmetric_memory as symm_mem
+
+                grp = self.group if self.group is not None else dist.group.WORLD
+                partial = symm_mem.empty((Mp, self.d), dtype=torch.bfloat16, device=dev)  # receive buffer
+                out = symm_mem.empty((Mp, self.d), dtype=torch.bfloat16, device=dev)
+                self._recv_hdl = symm_mem.rendezvous(partial, grp)
+                self._out_hdl = symm_mem.rendezvous(out, grp)
+            else:
+                partial = torch.empty((Mp, self.d), dtype=self.wire_dtype, device=dev)
+                out = torch.empty((Mp, self.d), dtype=torch.bfloat16, device=dev)
             ws = None
             if self._cuda:
                 from . import ops
@@ -122,6 +150,8 @@ class TensorParallelSwiGLU:
             return torch.empty((0, self.d), dtype=torch.bfloat16, device=self.device)
         partial, out, ws = self._buffers(M)
         bounds = self.slab_bounds(M)
+        if self.mode == "push" and self.world > 1:
+            return self._forward_push(x, partial, out, ws, bounds)
         compute = torch.cuda.current_stream(self.device) if self._cuda else None
         off = 0  # row offset in the (possibly padded) partial / out buffers
         for (r0, r1) in bounds:
@@ -143,18 +173,22 @@ class TensorParallelSwiGLU:
             else:
                 ctx = _NullCtx()
             with ctx:
+                bf16_wire = self.wire_dtype == torch.bfloat16
                 if self.world == 1:
-                    self.round_fn(p_slab, o_slab)
+                    o_slab.copy_(p_slab) if bf16_wire else self.round_fn(p_slab, o_slab)
                 elif self.mode == "allreduce":
                     dist.all_reduce(p_slab, op=dist.ReduceOp.SUM, group=self.group)
-                    self.round_fn(p_slab, o_slab)
+                    o_slab.copy_(p_slab) if bf16_wire else self.round_fn(p_slab, o_slab)
                 else:
                     per = rows_p // self.world
                     mine = p_slab[self.rank * per:(self.rank + 1) * per]
                     red = torch.empty_like(mine)
                     dist.reduce_scatter_tensor(red, p_slab, op=dist.ReduceOp.SUM, group=self.group)
-                    mine_bf16 = torch.empty((per, self.d), dtype=torch.bfloat16, device=self.device)
-                    self.round_fn(red, mine_bf16)
+                    if bf16_wire:
+                        mine_bf16 = red
+                    else:
+                        mine_bf16 = torch.empty((per, self.d), dtype=torch.bfloat16, device=self.device)
+                        self.round_fn(red, mine_bf16)
                     dist.all_gather_into_tensor(o_slab, mine_bf16, group=self.group)
             off += rows_p
         if self._cuda:
@@ -167,6 +201,64 @@ class TensorParallelSwiGLU:
                 rows_p = (rows + self.world - 1) // self.world * self.world
                 pieces.append(out[off:off + rows])
                 off += rows_p
+            return torch.cat(pieces, dim=0)
+        return out[:M]
+
+
+    def _forward_push(self, x, recv, out, ws, bounds):
+        """Reduce-scatter inside the down-GEMM epilogue (peer stores), then reduce + broadcast."""
+        import ctypes
+
+        from . import capi
+
+        M = x.size(0)
+        lib, world, rank, d, Fl = capi.lib, self.world, self.rank, self.d, self.F_local
+        compute = torch.cuda.current_stream(self.device)
+        comm = self._comm_stream
+        recv_bases = [int(p) for p in self._recv_hdl.buffer_ptrs]
+        out_bases = [int(p) for p in self._out_hdl.buffer_ptrs]
+        PtrArr = ctypes.c_void_p * world
+        vp = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+        off = 0
+        with torch.cuda.device(self.device):
+            for si, (r0, r1) in enumerate(bounds):
+                rows = r1 - r0
+                rows_p = (rows + world - 1) // world * world
+                rpo = rows_p // world
+                xs = x[r0:r1]
+                h = ws[: rows * Fl * 2].view(torch.bfloat16).view(rows, Fl)
+                sp = ctypes.c_void_p(compute.cuda_stream)
+                if self.trace is not None:
+                    self.trace("gateup_begin")
+                rc = lib.fswiglu_gateup_bf16(vp(xs), xs.stride(0), vp(self.w_gate), self.w_gate.stride(0), vp(self.w_up),
+                                             vp(h), Fl, rows, Fl, d, 0, sp)
+                capi.check(rc, "fswiglu_gateup_bf16")
+                if self.trace is not None:
+                    self.trace("gateup_end")
+                slab_bytes = off * d * 2
+                recv_ptrs = PtrArr(*[b + slab_bytes for b in recv_bases])
+                rc = lib.fswiglu_down_scatter_bf16(vp(h), Fl, vp(self.w_down), self.w_down.stride(0), recv_ptrs, world,
+                                                   rank, rpo, rows, d, Fl, sp)
+                capi.check(rc, "fswiglu_down_scatter_bf16")
+                ev = torch.cuda.Event()
+                ev.record(compute)
+                comm.wait_event(ev)
+                with torch.cuda.stream(comm):
+                    self._recv_hdl.barrier(channel=si % 4)  # every rank's partial rows of this slab have landed
+                    out_ptrs = PtrArr(*[b + (off + rank * rpo) * d * 2 for b in out_bases])
+                    rc = lib.fswiglu_reduce_bcast_bf16(ctypes.c_void_p(recv_bases[rank] + slab_bytes), out_ptrs, world,
+                                                       rpo, d, self._reduce_ctas, ctypes.c_void_p(comm.cuda_stream))
+                    capi.check(rc, "fswiglu_reduce_bcast_bf16")
+                off += rows_p
+            with torch.cuda.stream(comm):
+                self._out_hdl.barrier(channel=0)  # every rank's result rows have landed everywhere
+            compute.wait_stream(comm)
+        if out.size(0) != M:
+            pieces, off = [], 0
+            for (r0, r1) in bounds:
+                rows = r1 - r0
+                pieces.append(out[off:off + rows])
+                off += (rows + world - 1) // world * world
             return torch.cat(pieces, dim=0)
         return out[:M]
 

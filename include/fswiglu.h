@@ -134,6 +134,37 @@ int fswiglu_mlp_bf16_static(const void* x, int64_t ldx, const void* w_gate, cons
 int fswiglu_cast_f32_to_bf16(const void* src, void* dst, int64_t n, void* stream);
 
 /*
+ * Tensor-parallel reduction over peer memory, in two calls (no counterpart in the reference).
+ *
+ * fswiglu_down_scatter_bf16: the down projection of this rank's shard, out_partial = h Wd^T, whose
+ * epilogue is also the reduce-scatter: output row r belongs to rank r / rows_per_owner and its bf16
+ * partial sum is stored directly into that rank's receive buffer recv_ptrs[owner] (a peer-mapped
+ * device pointer; plain stores over NVLink, no TMA on peer memory), at row
+ * rank * rows_per_owner + r % rows_per_owner of a [world * rows_per_owner, d] matrix.  The transfer
+ * overlaps the GEMM tile by tile.  recv_ptrs is a HOST array of `world` (<= 8) device pointers.
+ *
+ * fswiglu_reduce_bcast_bf16: once every rank's stores have landed (the caller separates the two
+ * calls by a cross-rank barrier), each rank sums the `world` copies of its own `rows` rows in fp32
+ * in rank order, rounds once, and stores the result into every rank's output (out_ptrs[r] = base of
+ * rank r's output already offset to these rows).  A second barrier makes the outputs complete.
+ */
+int fswiglu_down_scatter_bf16(const void* h, int64_t ldh, const void* w_down, int64_t ldw,
+                              void* const* recv_ptrs, int world, int rank, int64_t rows_per_owner, int64_t M,
+                              int64_t d, int64_t F, void* stream);
+int fswiglu_reduce_bcast_bf16(const void* recv_local, void* const* out_ptrs, int world, int64_t rows, int64_t cols,
+                              int max_ctas, void* stream);
+
+/*
+ * Upper bound on the CTAs (= SMs, one persistent CTA each) the tiled GEMM kernels occupy; 0 restores
+ * "all SMs".  Tensor-parallel callers reserve a few SMs for the communication kernels that run
+ * beside the GEMMs: a persistent GEMM that holds every SM would keep a collective launched later
+ * from starting until the GEMM ends, and a collective that got there first would delay some of the
+ * GEMM's CTAs to the very end.  Process-wide setting; returns the previous value.  No counterpart in
+ * the reference (single GPU).
+ */
+int fswiglu_set_max_ctas(int max_ctas);
+
+/*
  * Device-side watchdog.  Kernels never spin forever: a wait that exceeds its limit records where it
  * gave up and the kernel unwinds.  This call synchronises `stream`, copies the status word of the
  * current device into *status (0 = healthy), clears it, and returns FSWIGLU_ERR_WATCHDOG if it

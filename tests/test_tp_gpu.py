@@ -87,7 +87,7 @@ def _worker(rank, world, port, mode, M, q):
 
 
 @pytest.mark.parametrize("world", [2, 4])
-@pytest.mark.parametrize("mode", ["allreduce", "rs_ag"])
+@pytest.mark.parametrize("mode", ["allreduce", "rs_ag", "push"])
 def test_nccl_ranks_match_oracle(world, mode):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
