@@ -51,8 +51,9 @@ constexpr int kStageBytes = kATileBytes + kBTileBytes;  // 48 KiB
 constexpr int kTmemCols = 512;
 constexpr int kGemmThreads = 192;
 constexpr int kNumEpilogueThreads = 128;
-// ring + 1 KiB alignment slack + barriers / bookkeeping
-constexpr int kGemmSmemBytes = kStages * kStageBytes + 1024 + 256;
+constexpr int kStoreStageBytes = 4 * 32 * 128;  // per epilogue warp: 32 rows x 128 bytes
+// ring + 1 KiB alignment slack + barriers / bookkeeping + store staging
+constexpr int kGemmSmemBytes = kStages * kStageBytes + 1024 + 256 + kStoreStageBytes;
 
 struct GemmParams {
   void* out;          // bf16 (or fp32 when kOutF32) [M, n_out], row stride ld_out elements
@@ -108,49 +109,94 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, const GemmParams& p) {
   return c;
 }
 
+// Output goes through a small shared-memory transpose so that global (or peer) stores are
+// coalesced: a thread owns one output ROW in TMEM, but a warp store instruction should cover whole
+// 128-byte lines of a few rows, not 16 bytes of 32 different rows (which matters most when the
+// destination is another GPU: NVLink moves 128-byte payloads far better than 16-byte ones).
+//
+// Staging tile of one epilogue warp: 32 rows x 128 bytes, 16-byte segments XOR-swizzled by (row & 7)
+// so that both the row-wise writes and the line-wise reads are bank-conflict free.
+//
+// stage_piece: this thread's `ncols` (16 or 32) consecutive outputs -> segments of its row, starting
+// at 16-byte segment `seg0`.
 template <bool kOutF32>
-__device__ __forceinline__ void store_chunk(const GemmParams& p, int row, int col0, int ncols,
+__device__ __forceinline__ void stage_piece(uint32_t warp_stage, uint32_t lane, int seg0, int ncols,
                                             const float (&v)[32]) {
-  // v holds `ncols` (16 or 32) consecutive output columns of one row, starting at col0.
-  if (row >= p.M || col0 >= p.n_out) return;
-  const int valid = min(ncols, p.n_out - col0);
-  long long lrow;
-  void* base = out_row_base(p, row, &lrow);
+  const uint32_t row_addr = warp_stage + lane * 128u;
   if constexpr (kOutF32) {
-    float* dst = reinterpret_cast<float*>(base) + lrow * p.ld_out + col0;
-    if (p.vec_ok && valid == ncols) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        if (4 * i < ncols)
-          reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        if (i < valid) dst[i] = v[i];
+    for (int i = 0; i < 8; ++i) {
+      if (4 * i < ncols) {
+        const uint32_t addr = row_addr + (static_cast<uint32_t>((seg0 + i) ^ (lane & 7u)) << 4);
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v[4 * i]), "f"(v[4 * i + 1]),
+                     "f"(v[4 * i + 2]), "f"(v[4 * i + 3])
+                     : "memory");
       }
     }
   } else {
-    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(base) + lrow * p.ld_out + col0;
-    if (p.vec_ok && valid == ncols) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        if (8 * i < ncols) {
-          uint4 q;
-          q.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
-          q.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
-          q.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
-          q.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
-          reinterpret_cast<uint4*>(dst)[i] = q;
-        }
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        if (i < valid) dst[i] = __float2bfloat16_rn(v[i]);
+    for (int i = 0; i < 4; ++i) {
+      if (8 * i < ncols) {
+        const uint32_t addr = row_addr + (static_cast<uint32_t>((seg0 + i) ^ (lane & 7u)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pack_bf16x2(v[8 * i], v[8 * i + 1])),
+                     "r"(pack_bf16x2(v[8 * i + 2], v[8 * i + 3])), "r"(pack_bf16x2(v[8 * i + 4], v[8 * i + 5])),
+                     "r"(pack_bf16x2(v[8 * i + 6], v[8 * i + 7]))
+                     : "memory");
       }
     }
   }
+}
+
+// drain_chunk: write the staged rows out.  `nsegs` 16-byte segments per row are valid, the chunk
+// starts at output column `col0`, the warp's first row is `row0`.  Lane l handles segment l % 8 of
+// rows l / 8, l / 8 + 4, ...: 8 lanes cover one 128-byte line.
+template <bool kOutF32>
+__device__ __forceinline__ void drain_chunk(const GemmParams& p, uint32_t warp_stage, uint32_t lane, int row0,
+                                            int col0, int nsegs) {
+  constexpr int kElemsPerSeg = kOutF32 ? 4 : 8;
+  const int seg = static_cast<int>(lane & 7u);
+  const int col = col0 + seg * kElemsPerSeg;
+  __syncwarp();
+  if (seg < nsegs && col < p.n_out) {
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int r = it * 4 + static_cast<int>(lane >> 3);
+      const int row = row0 + r;
+      if (row < p.M) {
+        const uint32_t addr = warp_stage + static_cast<uint32_t>(r) * 128u +
+                              (static_cast<uint32_t>(seg ^ (r & 7)) << 4);
+        uint4 q;
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "r"(addr));
+        long long lrow;
+        void* base = out_row_base(p, row, &lrow);
+        if constexpr (kOutF32) {
+          float* dst = reinterpret_cast<float*>(base) + lrow * p.ld_out + col;
+          if (p.vec_ok && col + 4 <= p.n_out) {
+            *reinterpret_cast<uint4*>(dst) = q;
+          } else {
+            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              if (col + e < p.n_out) dst[e] = __uint_as_float(w[e]);
+            }
+          }
+        } else {
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(base) + lrow * p.ld_out + col;
+          if (p.vec_ok && col + 8 <= p.n_out) {
+            *reinterpret_cast<uint4*>(dst) = q;
+          } else {
+            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+            unsigned short* d16 = reinterpret_cast<unsigned short*>(dst);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              if (col + e < p.n_out) d16[e] = static_cast<unsigned short>((w[e >> 1] >> ((e & 1) * 16)) & 0xffffu);
+            }
+          }
+        }
+      }
+    }
+  }
+  __syncwarp();
 }
 
 // 16 or 32 accumulator columns of this thread's row into r[0, ncols).
@@ -325,6 +371,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     // -------------------------------- epilogue --------------------------------
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
     const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t warp_stage = bar_base + 256u + static_cast<uint32_t>(quarter) * (32u * 128u);
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
@@ -336,13 +383,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       __syncwarp();
       tc_fence_after_sync();
       const uint32_t t_acc = tmem_base + lane_field + static_cast<uint32_t>(acc * kUmmaN);
-      const int row = tc.m_tile * kBlockM + quarter * 32 + static_cast<int>(lane);
-
+      const int row0 = tc.m_tile * kBlockM + quarter * 32;  // first output row of this warp
       const int col_base = tc.n_tile * p.tile_n;
+      // pieces of 32 output columns are staged; a chunk (128 bytes per row: 64 bf16 / 32 fp32
+      // columns) is drained as soon as it is complete
+      constexpr int kPiecesPerChunk = kOutF32 ? 1 : 2;
+      int piece = 0, chunk_col0 = col_base, chunk_segs = 0;
 #pragma unroll 1
       for (int c0 = 0; c0 < p.tile_n; c0 += 32) {
         if (col_base + c0 >= p.n_out) break;  // warp-uniform: the rest of the tile is past the edge
-        const int ncols = min(32, p.tile_n - c0);  // 32, or 16 for the last chunk of an odd width
+        const int ncols = min(32, p.tile_n - c0);  // 32, or 16 for the last piece of an odd width
         float v[32];
         if constexpr (kMode == kPlain) {
           uint32_t r[32];
@@ -350,7 +400,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-          store_chunk<kOutF32>(p, row, col_base + c0, ncols, v);
         } else if constexpr (kMode == kGatedSplit) {
           uint32_t g[32], u[32];
           tmem_ld_cols(t_acc + c0, ncols, g);             // gate columns [0, tile_n)
@@ -358,7 +407,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = silu_mul(__uint_as_float(g[i]), __uint_as_float(u[i]));
-          store_chunk<false>(p, row, col_base + c0, ncols, v);
         } else {
           // accumulator column 2j = up (linear), 2j+1 = gate (SiLU)
           uint32_t lo[32], hi[32];
@@ -375,9 +423,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             v[i] = silu_mul(__uint_as_float(lo[2 * i + 1]), __uint_as_float(lo[2 * i]));
             v[16 + i] = silu_mul(__uint_as_float(hi[2 * i + 1]), __uint_as_float(hi[2 * i]));
           }
-          store_chunk<false>(p, row, col_base + c0, ncols, v);
+        }
+        constexpr int kSegsPerPiece = kOutF32 ? 8 : 4;  // 32 columns
+        if (piece == 0) {
+          chunk_col0 = col_base + c0;
+          chunk_segs = 0;
+        }
+        stage_piece<kOutF32>(warp_stage, lane, piece * kSegsPerPiece, ncols, v);
+        chunk_segs += ncols / (kOutF32 ? 4 : 8);
+        if (++piece == kPiecesPerChunk) {
+          drain_chunk<kOutF32>(p, warp_stage, lane, row0, chunk_col0, chunk_segs);
+          piece = 0;
         }
       }
+      if (piece != 0) drain_chunk<kOutF32>(p, warp_stage, lane, row0, chunk_col0, chunk_segs);
       tc_fence_before_sync();
       mbar_arrive(tempty_bar(acc));
       acc ^= 1;
