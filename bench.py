@@ -245,7 +245,7 @@ def run_ours(args, rank, local_rank, world):
             capi.check(rc, "bench tp step")
 
         tp = TensorParallelSwiGLU(wg, wu, wd, n_slabs=args.slabs, mode=args.tp_mode, local_partial=local_partial,
-                                  comm_sms=args.comm_sms)
+                                  comm_sms=args.comm_sms, reduce_ctas=args.reduce_ctas)
         gateup_rows = max(r1 - r0 for r0, r1 in tp.slab_bounds(M))
         pending = []
 
@@ -312,14 +312,12 @@ def run_ours(args, rank, local_rank, world):
         rows_per = (M + world - 1) // world
         r0, r1 = min(M, rank * rows_per), min(M, (rank + 1) * rows_per)
         out_host = torch.empty((r1 - r0, d), dtype=torch.bfloat16).pin_memory()
-        x_dev = torch.empty_like(x)
 
         def e2e_step():
-            x_dev.copy_(x_host, non_blocking=True)
-            o = step(False)
-            out_host.copy_(o[r0:r1], non_blocking=True)
-            torch.cuda.synchronize(dev)
-        h2d, d2h = M * d * 2 * world, M * d * 2
+            tp.trace = None
+            tp.forward_from_host(x_host, out_host)
+        # per step: every rank reads its 1/world slice of x from the host and writes its slice of out
+        h2d, d2h = (M * d * 2 if args.tp_mode == "push" else M * d * 2 * world), M * d * 2
     for _ in range(3):
         e2e_step()
     barrier()
@@ -385,6 +383,7 @@ def main():
     ap.add_argument("--slabs", type=int, default=4)
     ap.add_argument("--tp-mode", choices=["allreduce", "rs_ag", "push"], default="push")
     ap.add_argument("--comm-sms", type=int, default=16, help="SMs left to the collective kernels when N > 1")
+    ap.add_argument("--reduce-ctas", type=int, default=0, help="CTAs of the reduce+broadcast kernel (0: = comm-sms)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))

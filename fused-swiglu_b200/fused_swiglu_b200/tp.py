@@ -64,7 +64,7 @@ class TensorParallelSwiGLU:
     def __init__(self, w_gate_shard: torch.Tensor, w_up_shard: torch.Tensor, w_down_shard: torch.Tensor,
                  group: Optional[dist.ProcessGroup] = None, n_slabs: int = 4, mode: str = "allreduce",
                  local_partial: Callable = _cuda_local_partial, round_fn: Callable = _cuda_round,
-                 comm_sms: int = 16, wire_dtype: torch.dtype = torch.float32):
+                 comm_sms: int = 16, wire_dtype: torch.dtype = torch.float32, reduce_ctas: int = 0):
         if mode not in ("allreduce", "rs_ag", "push"):
             raise ValueError("mode must be 'allreduce', 'rs_ag' or 'push'")
         if wire_dtype not in (torch.float32, torch.bfloat16):
@@ -83,7 +83,8 @@ class TensorParallelSwiGLU:
         self._bufs = {}
         self._cuda = self.device.type == "cuda"
         self._comm_stream = torch.cuda.Stream(device=self.device, priority=-1) if self._cuda else None
-        self._reduce_ctas = max(8, comm_sms)
+        self._reduce_ctas = reduce_ctas if reduce_ctas > 0 else max(8, comm_sms)
+        self._xin = None
         self.trace = None  # optional callable(tag): "gateup_begin" / "gateup_end" around that launch (push mode)
         if self._cuda and self.world > 1 and comm_sms > 0:
             # leave `comm_sms` SMs to the collective kernels that run beside the GEMMs (the launcher
@@ -204,6 +205,41 @@ class TensorParallelSwiGLU:
             return torch.cat(pieces, dim=0)
         return out[:M]
 
+
+    def forward_from_host(self, x_host: torch.Tensor, out_host: torch.Tensor) -> None:
+        """End-to-end step with host buffers.  x_host [M, d] is the (pinned) host copy of the replicated
+        input; out_host receives this rank's rows [rank*M/world, (rank+1)*M/world) of the result.
+
+        Every rank copies only its 1/world row slice over PCIe, then the slices are exchanged over
+        NVLink (copy engines writing into the peers' symmetric input buffers), so the host link
+        carries M*d*2/world bytes per rank instead of M*d*2.  Returns when out_host is filled."""
+        M = x_host.size(0)
+        world, rank = self.world, self.rank
+        per = (M + world - 1) // world
+        r0, r1 = min(M, rank * per), min(M, (rank + 1) * per)
+        if world == 1 or self.mode != "push":
+            x = x_host.to(self.device, non_blocking=True)
+            out = self.forward(x)
+            out_host.copy_(out[r0:r1], non_blocking=True)
+            torch.cuda.current_stream(self.device).synchronize()
+            return
+        import torch.distributed._symmetric_memory as symm_mem
+
+        if self._xin is None or self._xin[0].size(0) != M:
+            grp = self.group if self.group is not None else dist.group.WORLD
+            xin = symm_mem.empty((M, self.d), dtype=torch.bfloat16, device=self.device)
+            hdl = symm_mem.rendezvous(xin, grp)
+            peers = [hdl.get_buffer(p, (M, self.d), torch.bfloat16) for p in range(world)]
+            self._xin = (xin, hdl, peers)
+        xin, hdl, peers = self._xin
+        xin[r0:r1].copy_(x_host[r0:r1], non_blocking=True)           # PCIe: own slice only
+        for k in range(1, world):                                     # NVLink: slice to every peer
+            peers[(rank + k) % world][r0:r1].copy_(xin[r0:r1], non_blocking=True)
+        hdl.barrier(channel=1)                                        # all slices have landed here
+        out = self.forward(xin)
+        out_host.copy_(out[r0:r1], non_blocking=True)
+        hdl.barrier(channel=2)                                        # nobody overwrites xin while it is read
+        torch.cuda.current_stream(self.device).synchronize()
 
     def _forward_push(self, x, recv, out, ws, bounds):
         """Reduce-scatter inside the down-GEMM epilogue (peer stores), then reduce + broadcast."""

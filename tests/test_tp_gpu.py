@@ -79,6 +79,12 @@ def _worker(rank, world, port, mode, M, q):
         gathered = [torch.empty_like(out) for _ in range(world)]
         dist.all_gather(gathered, out)
         same = all(torch.equal(g, out) for g in gathered) and torch.equal(out, out2)
+        # host-buffer step: own slice over PCIe, the rest over NVLink, own slice of the result back
+        per = (M + world - 1) // world
+        r0, r1 = min(M, rank * per), min(M, (rank + 1) * per)
+        out_host = torch.empty((r1 - r0, out.size(1)), dtype=torch.bfloat16).pin_memory()
+        tp.forward_from_host(x.pin_memory(), out_host)
+        same = same and torch.equal(out_host, out[r0:r1].cpu())
         q.put((rank, "ok", m["rel_fro"], m["scaled_max_abs"], same, fsw.capi.device_status()))
     except Exception as e:  # noqa: BLE001
         q.put((rank, "error", repr(e)[:300], 0.0, False, -1))
