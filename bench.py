@@ -245,7 +245,8 @@ def run_ours(args, rank, local_rank, world):
             capi.check(rc, "bench tp step")
 
         tp = TensorParallelSwiGLU(wg, wu, wd, n_slabs=args.slabs, mode=args.tp_mode, local_partial=local_partial,
-                                  comm_sms=args.comm_sms, reduce_ctas=args.reduce_ctas)
+                                  comm_sms=args.comm_sms, reduce_ctas=args.reduce_ctas,
+                                  slab_rows=[int(v) for v in args.slab_rows.split(",")] if args.slab_rows else None)
         gateup_rows = max(r1 - r0 for r0, r1 in tp.slab_bounds(M))
         pending = []
 
@@ -264,7 +265,7 @@ def run_ours(args, rank, local_rank, world):
             record_flag["on"] = record
             return tp.forward(x)
         parallelism = f"tp{world} (Megatron: gate/up column-split, down row-split, {args.tp_mode}, " \
-                      f"{args.slabs} row slabs overlapped)"
+                      f"{len(tp.slab_bounds(M))} row slabs overlapped)"
 
     def barrier():
         if world > 1:
@@ -380,10 +381,11 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default=None)
     ap.add_argument("--e2e-steps", type=int, default=50)
-    ap.add_argument("--slabs", type=int, default=4)
+    ap.add_argument("--slabs", type=int, default=0, help="row slabs per step when N > 1 (0: planned from a cost model)")
     ap.add_argument("--tp-mode", choices=["allreduce", "rs_ag", "push"], default="push")
     ap.add_argument("--comm-sms", type=int, default=16, help="SMs left to the collective kernels when N > 1")
-    ap.add_argument("--reduce-ctas", type=int, default=0, help="CTAs of the reduce+broadcast kernel (0: = comm-sms)")
+    ap.add_argument("--reduce-ctas", type=int, default=32, help="CTAs of the reduce+broadcast kernel (0: = comm-sms)")
+    ap.add_argument("--slab-rows", type=str, default="", help="explicit slab heights, e.g. 3840,3840,512")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -48,6 +48,64 @@ def _cuda_round(src_f32, dst_bf16):
     capi.check(rc, "fswiglu_cast_f32_to_bf16")
 
 
+# ------------------------------------------------------------------------------------------------
+# Slab planner for the "push" mode.  Measured on 8 x B200 at the 70B shape, equal slabs lose time twice:
+# every slab's GEMMs end with a partly filled wave of the persistent schedule, and every slab boundary
+# costs launch gaps.  One large slab followed by a small one ([7168, 1024] rows) was 5 % faster than four
+# equal slabs: the large slab's reduction hides behind the small slab's GEMMs and only the small slab's
+# reduction is exposed.  The planner below picks the slab heights from a cost model of exactly these
+# effects (the GEMM tile model of pick_tile_n in csrc/api.cu + a compute/communication timeline).
+# ------------------------------------------------------------------------------------------------
+_UNIT_US = 1.375e-3       # one 128-byte operand row of one k-block, per CTA (measured: ~93 GB/s per SM)
+_LAUNCH_US = 8.0          # launch gaps of a slab's two GEMMs
+_BARRIER_US = 15.0        # cross-rank barrier before a slab's reduction
+_NVLINK_BYTES_PER_US = 6.0e5
+
+
+def _gemm_cost_units(m_tiles: int, n_out: int, max_tile: int, mma_per_col: int, ctas: int) -> float:
+    best = float("inf")
+    t = max_tile
+    while t >= 32 // mma_per_col:
+        waves = -(-(-(-n_out // t) * m_tiles) // ctas)
+        cost = waves * (128 + t * mma_per_col)
+        if cost < best * 0.97:
+            best = cost
+        t -= 16
+    return best
+
+
+def _slab_compute_us(rows: int, d: int, F_local: int, ctas: int) -> float:
+    m_tiles = -(-rows // 128)
+    gate_up = _gemm_cost_units(m_tiles, F_local, 128, 2, ctas) * -(-d // 64)
+    down = _gemm_cost_units(m_tiles, d, 256, 1, ctas) * -(-F_local // 64)
+    return (gate_up + down) * _UNIT_US + _LAUNCH_US
+
+
+def _timeline_us(rows_list, d, F_local, world, ctas) -> float:
+    compute_end = comm_end = 0.0
+    for rows in rows_list:
+        compute_end += _slab_compute_us(rows, d, F_local, ctas)
+        out_bytes = rows / world * d * 2 * (world - 1)
+        comm_end = max(compute_end, comm_end) + _BARRIER_US + out_bytes / _NVLINK_BYTES_PER_US
+    return comm_end
+
+
+def plan_slabs(M: int, d: int, F_local: int, world: int, ctas: int) -> list:
+    """Slab heights (rows) for the push mode: all but the last a multiple of 128 (hence of 8 * world)."""
+    if M <= 1024 or world == 1:
+        return [M]
+    best_rows, best_t = [M], _timeline_us([M], d, F_local, world, ctas)
+    for R in range(256, M, 128):
+        n = -(-M // R)
+        if n > 8:
+            continue
+        rows = [R] * (n - 1) + [M - R * (n - 1)]
+        t = _timeline_us(rows, d, F_local, world, ctas)
+        if t < best_t:
+            best_rows, best_t = rows, t
+    return best_rows
+
+
 class TensorParallelSwiGLU:
     """Rank-local shard of the MLP plus the collective that completes the forward.
 
@@ -62,9 +120,10 @@ class TensorParallelSwiGLU:
     """
 
     def __init__(self, w_gate_shard: torch.Tensor, w_up_shard: torch.Tensor, w_down_shard: torch.Tensor,
-                 group: Optional[dist.ProcessGroup] = None, n_slabs: int = 4, mode: str = "allreduce",
+                 group: Optional[dist.ProcessGroup] = None, n_slabs: int = 0, mode: str = "push",
                  local_partial: Callable = _cuda_local_partial, round_fn: Callable = _cuda_round,
-                 comm_sms: int = 16, wire_dtype: torch.dtype = torch.float32, reduce_ctas: int = 0):
+                 comm_sms: int = 16, wire_dtype: torch.dtype = torch.float32, reduce_ctas: int = 0,
+                 slab_rows: Optional[list] = None):
         if mode not in ("allreduce", "rs_ag", "push"):
             raise ValueError("mode must be 'allreduce', 'rs_ag' or 'push'")
         if wire_dtype not in (torch.float32, torch.bfloat16):
@@ -74,7 +133,9 @@ class TensorParallelSwiGLU:
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
-        self.n_slabs = max(1, n_slabs)
+        self.n_slabs_auto = n_slabs <= 0   # push mode: slab heights from plan_slabs()
+        self.n_slabs = max(1, n_slabs) if n_slabs > 0 else 4
+        self._gemm_ctas = 148
         self.mode = mode
         self.local_partial = local_partial
         self.round_fn = round_fn
@@ -85,6 +146,9 @@ class TensorParallelSwiGLU:
         self._comm_stream = torch.cuda.Stream(device=self.device, priority=-1) if self._cuda else None
         self._reduce_ctas = reduce_ctas if reduce_ctas > 0 else max(8, comm_sms)
         self._xin = None
+        # explicit slab heights (rows), e.g. [3840, 3840, 512]; every slab but the last must be a
+        # multiple of 8 * world.  None: n_slabs equal slabs.
+        self.slab_rows = list(slab_rows) if slab_rows else None
         self.trace = None  # optional callable(tag): "gateup_begin" / "gateup_end" around that launch (push mode)
         if self._cuda and self.world > 1 and comm_sms > 0:
             # leave `comm_sms` SMs to the collective kernels that run beside the GEMMs (the launcher
@@ -92,7 +156,8 @@ class TensorParallelSwiGLU:
             from . import capi
 
             sms = torch.cuda.get_device_properties(self.device).multi_processor_count
-            capi.lib.fswiglu_set_max_ctas(max(1, sms - comm_sms))
+            self._gemm_ctas = max(1, sms - comm_sms)
+            capi.lib.fswiglu_set_max_ctas(self._gemm_ctas)
 
     @classmethod
     def from_full(cls, w_gate, w_up, w_down, device, group=None, **kw):
@@ -104,8 +169,21 @@ class TensorParallelSwiGLU:
 
     # slab r0:r1 boundaries; with rs_ag every slab must split evenly over the ranks
     def slab_bounds(self, M: int):
-        n = min(self.n_slabs, max(1, M))
         quantum = self.world * 8 if self.mode in ("rs_ag", "push") else 1
+        if self.slab_rows and sum(self.slab_rows) == M and all(r > 0 for r in self.slab_rows) and \
+                all(r % quantum == 0 for r in self.slab_rows[:-1]):
+            bounds, r0 = [], 0
+            for r in self.slab_rows:
+                bounds.append((r0, r0 + r))
+                r0 += r
+            return bounds
+        if self.mode == "push" and self.world > 1 and self.n_slabs_auto and 128 % quantum == 0:
+            bounds, r0 = [], 0
+            for r in plan_slabs(M, self.d, self.F_local, self.world, self._gemm_ctas):
+                bounds.append((r0, r0 + r))
+                r0 += r
+            return bounds
+        n = min(self.n_slabs, max(1, M))
         per = (M + n - 1) // n
         per = (per + quantum - 1) // quantum * quantum
         bounds = []
