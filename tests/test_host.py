@@ -128,3 +128,32 @@ def test_tp_slab_bounds_cover_rows():
             assert b[0][0] == 0 and b[-1][1] == M
             assert all(x[1] == y[0] for x, y in zip(b, b[1:]))
             assert len(b) <= 4
+
+
+def test_slab_planner_properties():
+    from fused_swiglu_b200.tp import plan_slabs
+
+    for (M, d, Fl, world) in [(8192, 8192, 3584, 8), (8192, 8192, 14336, 2), (32414, 5120, 1728, 8), (4096, 4096, 5504, 2),
+                              (1000, 4096, 1376, 8), (1, 64, 8, 2)]:
+        rows = plan_slabs(M, d, Fl, world, 132)
+        assert sum(rows) == M and all(r > 0 for r in rows) and len(rows) <= 8
+        assert all(r % (8 * world) == 0 for r in rows[:-1])
+    # the measured optimum at the 70B shape on 8 GPUs
+    assert plan_slabs(8192, 8192, 3584, 8, 132) == [7168, 1024]
+    assert plan_slabs(512, 4096, 1376, 8, 132) == [512]
+
+
+def test_bench_reference_arm_prints_one_json_line():
+    import json
+    import subprocess
+    import sys
+
+    res = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "2",
+                          "--warmup", "1"], capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr[-500:]
+    lines = [ln for ln in res.stdout.splitlines() if ln.startswith("{")]
+    assert len(lines) == 1
+    j = json.loads(lines[0])
+    assert j["impl"] == "reference" and j["unit"] == "TFLOP/s" and j["value"] > 0
+    assert j["cpu_baseline"]["kind"] == "port" and j["e2e"]["h2d_bytes_per_step"] == 0
+    assert j["config"]["workload"] == "c2_llama2_7b_prefill"

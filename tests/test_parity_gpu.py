@@ -320,3 +320,53 @@ def test_launches_are_counted(fsw, cuda_dev):
     fsw.ops.fused_swiglu_mlp_bf16(x, wg, wu, wd)
     assert fsw.capi.launch_count() - before >= 1
     healthy(fsw)
+
+
+def test_push_reduction_kernels_on_one_gpu(fsw, cuda_dev):
+    """The tensor-parallel 'push' kernels with all ranks emulated on ONE device, one after the other
+    (no kernel waits for another): every rank's down GEMM scatters its bf16 partial rows into the
+    owners' receive buffers, then every owner reduces its rows in fp32 and stores the result into
+    all outputs.  Checked against the fp32 expression and for identical outputs on all 'ranks'."""
+    import ctypes
+    lib, capi = fsw.capi.lib, fsw.capi
+    world, M, d, F = 4, 520, 264, 1096          # ragged: 520 rows -> 130 per owner, F/4 = 274 -> 280/280/280/256
+    x, wg, wu, wd = fsw.inputs.make_mlp_inputs(M, d, F, seed=12)
+    rpo = (M + world - 1) // world
+    xd = x.to(cuda_dev)
+    recv = [torch.full((world, rpo, d), float("nan"), dtype=torch.bfloat16, device=cuda_dev) for _ in range(world)]
+    outs = [torch.full((world * rpo, d), float("nan"), dtype=torch.bfloat16, device=cuda_dev) for _ in range(world)]
+    PtrArr = ctypes.c_void_p * world
+    recv_ptrs = PtrArr(*[t.data_ptr() for t in recv])
+    for r in range(world):
+        g, u, dn = (t.to(cuda_dev) for t in fsw.pack.shard_mlp_weights(wg, wu, wd, world, r))
+        h = fsw.ops.fused_swiglu_gateup_bf16(xd, g, u)
+        rc = lib.fswiglu_down_scatter_bf16(ctypes.c_void_p(h.data_ptr()), h.size(1), ctypes.c_void_p(dn.data_ptr()),
+                                           dn.size(1), recv_ptrs, world, r, rpo, M, d, h.size(1), None)
+        assert rc == capi.OK, capi.status_string(rc)
+    torch.cuda.synchronize()
+    for o in range(world):
+        out_ptrs = PtrArr(*[t.data_ptr() + o * rpo * d * 2 for t in outs])
+        rc = lib.fswiglu_reduce_bcast_bf16(ctypes.c_void_p(recv[o].data_ptr()), out_ptrs, world, rpo, d, 16, None)
+        assert rc == capi.OK, capi.status_string(rc)
+    healthy(fsw)
+    for t in outs[1:]:
+        assert torch.equal(t[:M], outs[0][:M])
+    ref = orc.mlp_fp32(*[f32(t) for t in (x, wg, wu, wd)])
+    m = orc.error_metrics(f32(outs[0][:M]), ref)
+    # bf16 partials on the wire + fp32 accumulation + one rounding
+    assert m["rel_fro"] <= REL_FRO_GRADED and m["scaled_max_abs"] <= SCALED_MAX_ABS, m
+    # bad arguments are refused before anything is launched
+    assert lib.fswiglu_down_scatter_bf16(None, 8, None, 8, recv_ptrs, 9, 0, 8, 8, 8, 8, None) == capi.ERR_BAD_ARG
+    assert lib.fswiglu_reduce_bcast_bf16(None, out_ptrs, 4, 0, 8, 0, None) == capi.OK
+
+
+def test_sm_budget_changes_nothing_but_the_grid(fsw, cuda_dev):
+    x, wg, wu, wd = (t.to(cuda_dev) for t in fsw.inputs.make_mlp_inputs(700, 256, 520, seed=13))
+    want = fsw.ops.fused_swiglu_mlp_bf16(x, wg, wu, wd)
+    prev = fsw.capi.lib.fswiglu_set_max_ctas(100)
+    try:
+        got = fsw.ops.fused_swiglu_mlp_bf16(x, wg, wu, wd)
+    finally:
+        fsw.capi.lib.fswiglu_set_max_ctas(prev)
+    healthy(fsw)
+    assert torch.equal(got, want)
