@@ -3,7 +3,7 @@
 Rank r keeps rows [lo, hi) of W_gate / W_up (column-parallel: it owns h[:, lo:hi], no
 communication) and columns [lo, hi) of W_down (row-parallel), so it produces a full-shape
 partial out_r [M, d]; the MLP output is the sum over ranks.  The reference has no multi-GPU
-code at all; this is the layout BASELINE's 70B and ragged configurations prescribe.
+code at all; this is the layout the 70B-shape and ragged-batch benchmark configurations prescribe.
 
 Numerics: partial sums leave the down GEMM in fp32, are summed in fp32 by the collective,
 and are rounded to bf16 once at the end, which keeps the relative Frobenius error at the

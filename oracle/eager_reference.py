@@ -1,12 +1,12 @@
 """The reference's eager PyTorch expressions, runnable on CPU.  TEST INFRASTRUCTURE ONLY.
 
-These are the expressions the reference project checks its kernel against and that the build is
-graded on; nothing that ships may import this file (it is used by tests/, by the fixture
+These are the expressions the reference project checks its kernel against and that this
+library's results are held to; nothing that ships may import this file (it is used by tests/, by the fixture
 generator tests/golden/make_golden.py and by the cpu_baseline / reference legs of bench.py).
 
   gateup_interleaved_eager : numeric_tests.py:41-43 (twin: bench_swiglu.py:30-32)
   mlp_eager                : (F.silu(x @ Wg.T) * (x @ Wu.T)) @ Wd.T, the whole-MLP expression
-                             of BASELINE configs[0] (the reference itself stops after the gate)
+                             of the benchmark's first configuration (the reference itself stops after the gate)
 """
 from __future__ import annotations
 

@@ -12,7 +12,7 @@ What is restated here (numpy, fp32 arithmetic, explicit bf16 rounding points):
   * the arithmetic of the reference kernel's epilogue, csrc/SwiGLU/swiglu.cu:376-383 and :96
         out = bf16( acc[:, 2c] * silu(acc[:, 2c+1]) ),  acc in fp32, silu(v) = v / (1 + exp(-v))
     -> gateup_interleaved_fp32acc / gateup_split_fp32acc (one rounding, at the end)
-  * the whole-MLP expression the build is graded on (BASELINE configs[0]):
+  * the whole-MLP expression results are checked against (the benchmark's first configuration):
         out = (silu(x Wg^T) * (x Wu^T)) Wd^T  in fp32                -> mlp_fp32
     and the same with the rounding points of the GPU path (h rounded to bf16 between the
     two GEMMs, result rounded to bf16)                               -> mlp_bf16_pipeline
@@ -97,7 +97,7 @@ def gateup_split_fp32acc(x: np.ndarray, w_gate: np.ndarray, w_up: np.ndarray, ro
 # whole MLP
 # ----------------------------------------------------------------------------------------
 def mlp_fp32(x: np.ndarray, w_gate: np.ndarray, w_up: np.ndarray, w_down: np.ndarray) -> np.ndarray:
-    """(silu(x Wg^T) * (x Wu^T)) Wd^T entirely in fp32: the graded expression."""
+    """(silu(x Wg^T) * (x Wu^T)) Wd^T entirely in fp32: the expression results are held to."""
     h = silu(_mm(x, w_gate)) * _mm(x, w_up)
     return _mm(h, w_down)
 

@@ -2,7 +2,7 @@
 
 The reference ships no known-answer vectors, so the fixtures are outputs of the reference's
 own eager PyTorch expressions (numeric_tests.py:41-43 for the packed gate-up op; the whole-MLP
-expression (F.silu(x@Wg.T) * (x@Wu.T)) @ Wd.T of BASELINE configs[0]) executed by PyTorch on
+expression (F.silu(x@Wg.T) * (x@Wu.T)) @ Wd.T of the benchmark's first configuration) executed by PyTorch on
 CPU, on seeded inputs.  Re-run with:   python tests/golden/make_golden.py
 bf16 tensors are stored as uint16 bit patterns, everything else as fp32.
 
