@@ -235,6 +235,28 @@ int pick_tile_n(int num_m_tiles, int64_t n_out, int max_tile, int mma_per_col, i
   return best < needed ? best : (needed < 16 ? 16 : needed);
 }
 
+// Tail split (see GemmParams::split_from): on when FSWIGLU_TAIL_SPLIT=1, off when =0.
+constexpr bool kTailSplitDefault = false;
+bool tail_split_enabled() {
+  const char* env = std::getenv("FSWIGLU_TAIL_SPLIT");
+  if (env == nullptr || env[0] == '\0') return kTailSplitDefault;
+  return env[0] != '0';
+}
+
+// Decide whether the tiles of the last, partly filled wave are processed as half-width units:
+// worth it when that wave fills at most half of the CTAs (two units per tile still fit in one wave).
+void plan_tail_split(GemmParams* p, int ctas) {
+  const int tiles = p->num_m_tiles * p->num_n_tiles;
+  p->split_from = tiles;
+  p->half_boxes = 0;
+  if (!tail_split_enabled() || p->tile_n % 32 != 0 || tiles <= ctas) return;
+  const int rem = tiles % ctas;
+  if (rem > 0 && 2 * rem <= ctas) {
+    p->split_from = tiles - rem;
+    p->half_boxes = 1;
+  }
+}
+
 int effective_ctas(const DeviceState& st) {
   const int cap = g_max_ctas.load(std::memory_order_relaxed);
   return (cap > 0 && cap < st.num_sms) ? cap : st.num_sms;
@@ -244,10 +266,9 @@ template <int kMode, bool kOutF32>
 int launch_gemm(const DeviceState& st, const CUtensorMap& ma, const CUtensorMap& mb0,
                 const CUtensorMap& mb1, const GemmParams& p, cudaStream_t stream) {
   const int tiles = p.num_m_tiles * p.num_n_tiles;
-  int ctas = st.num_sms;
-  const int cap = g_max_ctas.load(std::memory_order_relaxed);
-  if (cap > 0 && cap < ctas) ctas = cap;
-  const int grid = tiles < ctas ? tiles : ctas;
+  const int units = p.split_from + 2 * (tiles - p.split_from);
+  const int ctas = effective_ctas(st);
+  const int grid = units < ctas ? units : ctas;
   gemm_tcgen05_kernel<kMode, kOutF32><<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(ma, mb0, mb1, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError() == cudaSuccess ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
@@ -277,14 +298,16 @@ int gateup_impl(DeviceState& st, const void* x, int64_t ldx, const void* w0, int
   p.num_m_tiles = static_cast<int>((M + 127) / 128);
   p.tile_n = pick_tile_n(p.num_m_tiles, F, 128, 2, effective_ctas(st));
   p.num_n_tiles = static_cast<int>((F + p.tile_n - 1) / p.tile_n);
+  plan_tail_split(&p, effective_ctas(st));
+  const int box_cols = p.half_boxes ? p.tile_n / 2 : p.tile_n;  // output columns covered by one B box
   CUtensorMap ma, mb0, mb1;
   if ((rc = encode_map(&ma, x, M, d, ldx, 128))) return rc;
   if (interleaved) {
-    if ((rc = encode_map(&mb0, w0, 2 * F, d, ldw, 2 * p.tile_n))) return rc;
+    if ((rc = encode_map(&mb0, w0, 2 * F, d, ldw, 2 * box_cols))) return rc;
     mb1 = mb0;
   } else {
-    if ((rc = encode_map(&mb0, w0, F, d, ldw, p.tile_n))) return rc;
-    if ((rc = encode_map(&mb1, w_up, F, d, ldw, p.tile_n))) return rc;
+    if ((rc = encode_map(&mb0, w0, F, d, ldw, box_cols))) return rc;
+    if ((rc = encode_map(&mb1, w_up, F, d, ldw, box_cols))) return rc;
   }
   p.group_m = pick_group_m(p.num_m_tiles, d);
   p.vec_ok = (aligned16(h) && ldh % 8 == 0) ? 1 : 0;
@@ -311,9 +334,10 @@ int down_impl(DeviceState& st, const void* h, int64_t ldh, const void* w_down, i
   p.num_m_tiles = static_cast<int>((M + 127) / 128);
   p.tile_n = pick_tile_n(p.num_m_tiles, d, 256, 1, effective_ctas(st));
   p.num_n_tiles = static_cast<int>((d + p.tile_n - 1) / p.tile_n);
+  plan_tail_split(&p, effective_ctas(st));
   CUtensorMap ma, mb;
   if ((rc = encode_map(&ma, h, M, F, ldh, 128))) return rc;
-  if ((rc = encode_map(&mb, w_down, d, F, ldw, p.tile_n))) return rc;
+  if ((rc = encode_map(&mb, w_down, d, F, ldw, p.half_boxes ? p.tile_n / 2 : p.tile_n))) return rc;
   p.group_m = pick_group_m(p.num_m_tiles, F);
   const bool f32 = out_dtype == FSWIGLU_OUT_F32;
   p.vec_ok = (aligned16(out) && ldo % (f32 ? 4 : 8) == 0) ? 1 : 0;
@@ -662,9 +686,10 @@ int fswiglu_down_scatter_bf16(const void* h, int64_t ldh, const void* w_down, in
   p.scatter_world = world;
   p.scatter_rank = rank;
   p.rows_per_owner = static_cast<int>(rows_per_owner);
+  plan_tail_split(&p, effective_ctas(*st));
   CUtensorMap ma, mb;
   if ((rc = encode_map(&ma, h, M, F, ldh, 128))) return rc;
-  if ((rc = encode_map(&mb, w_down, d, F, ldw, p.tile_n))) return rc;
+  if ((rc = encode_map(&mb, w_down, d, F, ldw, p.half_boxes ? p.tile_n / 2 : p.tile_n))) return rc;
   return launch_gemm<kPlain, false>(*st, ma, mb, mb, p, static_cast<cudaStream_t>(stream));
 }
 

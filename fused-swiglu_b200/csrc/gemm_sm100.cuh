@@ -66,6 +66,12 @@ struct GemmParams {
   int num_n_tiles;
   int group_m;        // rasterisation: this many M-tiles share a sweep over N
   int vec_ok;         // 1 when every row start of `out` is 16-byte aligned
+  // Tail split: tiles with index >= split_from (the partly filled last wave of the persistent
+  // schedule) are processed as two half-width units each, so that twice as many SMs share that
+  // wave.  split_from == number of tiles disables it.  With half_boxes != 0 the B tensor maps are
+  // encoded with boxes of half a tile's rows and a full-width tile takes two boxes per matrix.
+  int split_from;
+  int half_boxes;
   uint32_t* status;   // device watchdog word (0 = healthy)
   // Tensor-parallel reduce-scatter by direct stores (plain mode, bf16 out): when scatter_world > 0
   // output row r belongs to rank r / rows_per_owner and is written straight into that rank's
@@ -119,6 +125,27 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, const GemmParams& p) {
 //
 // stage_piece: this thread's `ncols` (16 or 32) consecutive outputs -> segments of its row, starting
 // at 16-byte segment `seg0`.
+// One unit of work: a whole tile, or the left / right half of a tail tile.
+struct Unit {
+  int m_tile;
+  int col0;   // first output column
+  int width;  // output columns (tile_n or tile_n / 2)
+};
+__device__ __forceinline__ Unit unit_coord(int u, const GemmParams& p) {
+  int tile = u, half = -1;
+  if (u >= p.split_from) {
+    const int s = u - p.split_from;
+    tile = p.split_from + (s >> 1);
+    half = s & 1;
+  }
+  const TileCoord tc = tile_coord(tile, p);
+  Unit r;
+  r.m_tile = tc.m_tile;
+  r.width = half < 0 ? p.tile_n : p.tile_n / 2;
+  r.col0 = tc.n_tile * p.tile_n + (half > 0 ? p.tile_n / 2 : 0);
+  return r;
+}
+
 template <bool kOutF32>
 __device__ __forceinline__ void stage_piece(uint32_t warp_stage, uint32_t lane, int seg0, int ncols,
                                             const float (&v)[32]) {
@@ -261,9 +288,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   const uint32_t tmem_base = *tmem_ptr_slot;
 
   const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+  const int num_units = p.split_from + 2 * (num_tiles - p.split_from);
   const int num_kb = (p.K + kBlockK - 1) / kBlockK;
-  const int umma_n = (kMode == kPlain) ? p.tile_n : 2 * p.tile_n;  // accumulator columns in use
-  const uint32_t stage_tx_bytes = kATileBytes + static_cast<uint32_t>(umma_n) * (kBlockK * 2);
+  // MMA N extent (= accumulator columns in use, = B rows in shared memory) of a unit of `width` columns
+  auto mma_n_of = [&](int width) { return (kMode == kPlain) ? width : 2 * width; };
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -272,12 +300,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       uint32_t phase = 0;
       uint32_t issued_mask = 0, last_parity_mask = 0;
       bool alive = true;
-      for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
-        const TileCoord tc = tile_coord(tile, p);
-        const int m0 = tc.m_tile * kBlockM;
-        // first B row of this tile: rows of W (plain), of W_gate and W_up (split), or of the
+      for (int unit = blockIdx.x; unit < num_units && alive; unit += gridDim.x) {
+        const Unit un = unit_coord(unit, p);
+        const int m0 = un.m_tile * kBlockM;
+        // first B row of this unit: rows of W (plain), of W_gate and W_up (split), or of the
         // packed W1W3 (interleaved: two rows per output column)
-        const int b_row = tc.n_tile * (kMode == kGatedInterleaved ? 2 * p.tile_n : p.tile_n);
+        const int b_row = (kMode == kGatedInterleaved) ? 2 * un.col0 : un.col0;
+        const uint32_t stage_tx_bytes = kATileBytes + static_cast<uint32_t>(mma_n_of(un.width)) * (kBlockK * 2);
+        // a full-width tile needs two boxes per matrix when the maps hold half-width boxes
+        const bool two_boxes = p.half_boxes != 0 && un.width == p.tile_n;
+        const int half_rows = (kMode == kGatedInterleaved) ? p.tile_n : p.tile_n / 2;  // rows of a half box
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!wd.wait(empty_bar(stage), phase ^ 1u, kSiteProducerEmpty)) {
             alive = false;
@@ -288,9 +320,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
           mbar_arrive_expect_tx(full_bar(stage), stage_tx_bytes);
           tma_load_2d(a_dst, &map_a, full_bar(stage), kb * kBlockK, m0);
           tma_load_2d(b_dst, &map_b0, full_bar(stage), kb * kBlockK, b_row);
+          if (two_boxes) {
+            tma_load_2d(b_dst + half_rows * (kBlockK * 2), &map_b0, full_bar(stage), kb * kBlockK, b_row + half_rows);
+          }
           if (kMode == kGatedSplit) {
-            // W_up rows go right behind the W_gate rows (tile_n * 128 bytes, a multiple of 1024)
-            tma_load_2d(b_dst + p.tile_n * (kBlockK * 2), &map_b1, full_bar(stage), kb * kBlockK, b_row);
+            // W_up rows go right behind the W_gate rows (width * 128 bytes, a multiple of 1024)
+            const uint32_t up_dst = b_dst + un.width * (kBlockK * 2);
+            tma_load_2d(up_dst, &map_b1, full_bar(stage), kb * kBlockK, b_row);
+            if (two_boxes) {
+              tma_load_2d(up_dst + half_rows * (kBlockK * 2), &map_b1, full_bar(stage), kb * kBlockK, b_row + half_rows);
+            }
           }
           issued_mask |= 1u << stage;
           last_parity_mask = (last_parity_mask & ~(1u << stage)) | (phase << stage);
@@ -319,13 +358,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
     if (lane == 0) {
-      const uint32_t idesc = umma_idesc_bf16_f32(kBlockM, umma_n);
+      const uint32_t idesc_full = umma_idesc_bf16_f32(kBlockM, mma_n_of(p.tile_n));
+      const uint32_t idesc_half = umma_idesc_bf16_f32(kBlockM, mma_n_of(p.tile_n / 2));
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool alive = true;
-      for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+      for (int unit = blockIdx.x; unit < num_units && alive; unit += gridDim.x) {
+        const uint32_t idesc = unit < p.split_from ? idesc_full : idesc_half;
         if (!wd.wait(tempty_bar(acc), acc_phase ^ 1u, kSiteMmaTmemEmpty)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kUmmaN);
@@ -374,8 +415,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     const uint32_t warp_stage = bar_base + 256u + static_cast<uint32_t>(quarter) * (32u * 128u);
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      const TileCoord tc = tile_coord(tile, p);
+    for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x) {
+      const Unit un = unit_coord(unit, p);
       uint32_t ok = 1;
       if (lane == 0) ok = wd.wait(tfull_bar(acc), acc_phase, kSiteEpilogueFull) ? 1u : 0u;
       ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -383,16 +424,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       __syncwarp();
       tc_fence_after_sync();
       const uint32_t t_acc = tmem_base + lane_field + static_cast<uint32_t>(acc * kUmmaN);
-      const int row0 = tc.m_tile * kBlockM + quarter * 32;  // first output row of this warp
-      const int col_base = tc.n_tile * p.tile_n;
+      const int row0 = un.m_tile * kBlockM + quarter * 32;  // first output row of this warp
+      const int col_base = un.col0;
+      const int width = un.width;
       // pieces of 32 output columns are staged; a chunk (128 bytes per row: 64 bf16 / 32 fp32
       // columns) is drained as soon as it is complete
       constexpr int kPiecesPerChunk = kOutF32 ? 1 : 2;
       int piece = 0, chunk_col0 = col_base, chunk_segs = 0;
 #pragma unroll 1
-      for (int c0 = 0; c0 < p.tile_n; c0 += 32) {
+      for (int c0 = 0; c0 < width; c0 += 32) {
         if (col_base + c0 >= p.n_out) break;  // warp-uniform: the rest of the tile is past the edge
-        const int ncols = min(32, p.tile_n - c0);  // 32, or 16 for the last piece of an odd width
+        const int ncols = min(32, width - c0);  // 32, or 16 for the last piece of an odd width
         float v[32];
         if constexpr (kMode == kPlain) {
           uint32_t r[32];
@@ -402,8 +444,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
         } else if constexpr (kMode == kGatedSplit) {
           uint32_t g[32], u[32];
-          tmem_ld_cols(t_acc + c0, ncols, g);             // gate columns [0, tile_n)
-          tmem_ld_cols(t_acc + p.tile_n + c0, ncols, u);  // up columns [tile_n, 2 tile_n)
+          tmem_ld_cols(t_acc + c0, ncols, g);             // gate columns [0, width)
+          tmem_ld_cols(t_acc + width + c0, ncols, u);     // up columns [width, 2 width)
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = silu_mul(__uint_as_float(g[i]), __uint_as_float(u[i]));
