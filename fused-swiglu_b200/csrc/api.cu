@@ -405,6 +405,13 @@ int decode_impl(DeviceState& st, const void* x, int64_t ldx, const void* w_gate,
   void* args[] = {&m_gate, &m_up, &m_down, &m_x, &m_h, &p};
   const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(decode_fused_kernel), dim3(grid),
                                                     dim3(kDecThreads), args, kDecSmemBytes, stream);
+  if (e == cudaErrorCooperativeLaunchTooLarge) {
+    // Not every CTA can be resident right now (SMs held by someone else): the hand-over inside the
+    // kernel would not be safe, so the launch was refused.  The tiled kernels need no co-residency.
+    (void)cudaGetLastError();
+    if ((rc = gateup_impl(st, x, ldx, w_gate, ldw_gu, w_up, h, F, M, F, d, 0, stream))) return rc;
+    return down_impl(st, h, F, w_down, ldw_d, out, ldo, M, d, F, out_dtype, stream);
+  }
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return e == cudaSuccess ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
 }

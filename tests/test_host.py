@@ -157,3 +157,20 @@ def test_bench_reference_arm_prints_one_json_line():
     assert j["impl"] == "reference" and j["unit"] == "TFLOP/s" and j["value"] > 0
     assert j["cpu_baseline"]["kind"] == "port" and j["e2e"]["h2d_bytes_per_step"] == 0
     assert j["config"]["workload"] == "c2_llama2_7b_prefill"
+
+
+def test_torch_extension_surface_loads_without_a_gpu():
+    """The drop-in module imports on a CPU-only box and registers the reference's names and schemas
+    (csrc/torch_bindings.cpp:31-50 of the reference); calling an op there fails loudly."""
+    import fused_mlp_module
+
+    for name in ("fused_swiglu_bf16", "swiglu_fwd_bf16", "fused_swiglu_gateup_bf16", "swiglu_down_bf16",
+                 "fused_swiglu_mlp_bf16"):
+        assert callable(getattr(fused_mlp_module, name))
+        assert hasattr(torch.ops.ASMLLM, name)
+    assert "Tensor X, Tensor W1W3" in str(torch.ops.ASMLLM.fused_swiglu_bf16.default._schema)
+    assert "int m, int n, int k, Tensor A, int ldA, Tensor B, int ldB, Tensor C, int ldC" in \
+        str(torch.ops.ASMLLM.swiglu_fwd_bf16.default._schema)
+    with pytest.raises(RuntimeError):
+        fused_mlp_module.fused_swiglu_bf16(torch.zeros((4, 8), dtype=torch.bfloat16),
+                                           torch.zeros((8, 8), dtype=torch.bfloat16))
