@@ -15,6 +15,7 @@
 
 #include "../../include/fswiglu.h"
 #include "decode_sm100.cuh"
+#include "gemm_pair_sm100.cuh"
 #include "gemm_sm100.cuh"
 
 namespace fsw {
@@ -154,6 +155,10 @@ int device_state(DeviceState** out) {
     e = e ? e : opt_in_smem(gemm_tcgen05_kernel<kGatedSplit, false>, kGemmSmemBytes);
     e = e ? e : opt_in_smem(gemm_tcgen05_kernel<kGatedInterleaved, false>, kGemmSmemBytes);
     e = e ? e : decode_opt_in_smem();
+    e = e ? e : opt_in_smem(gemm_pair_kernel<kPlain, false>, kPairSmemBytes);
+    e = e ? e : opt_in_smem(gemm_pair_kernel<kPlain, true>, kPairSmemBytes);
+    e = e ? e : opt_in_smem(gemm_pair_kernel<kGatedSplit, false>, kPairSmemBytes);
+    e = e ? e : opt_in_smem(gemm_pair_kernel<kGatedInterleaved, false>, kPairSmemBytes);
     if (e != cudaSuccess) return FSWIGLU_ERR_CUDA;
     st.ready = true;
   }
@@ -274,6 +279,36 @@ int launch_gemm(const DeviceState& st, const CUtensorMap& ma, const CUtensorMap&
   return cudaGetLastError() == cudaSuccess ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
 }
 
+// Two-SM kernel (gemm_pair_sm100.cuh): experimental, selected with FSWIGLU_PAIR=1 for M > 128.
+bool pair_enabled() {
+  const char* env = std::getenv("FSWIGLU_PAIR");
+  return env != nullptr && env[0] == '1';
+}
+
+// `p` arrives filled for the one-SM kernel; re-plan it for 256-row pair tiles of full width.
+template <int kMode, bool kOutF32>
+int launch_gemm_pair(const DeviceState& st, const void* a, int64_t lda, const void* b0, const void* b1, int64_t ldb,
+                     int64_t b_rows, GemmParams p, cudaStream_t stream) {
+  p.tile_n = (kMode == kPlain) ? 256 : 128;
+  p.num_m_tiles = (p.M + 255) / 256;
+  p.num_n_tiles = (p.n_out + p.tile_n - 1) / p.tile_n;
+  p.group_m = pick_group_m(2 * p.num_m_tiles, p.K) / 2;
+  if (p.group_m < 1) p.group_m = 1;
+  p.split_from = p.num_m_tiles * p.num_n_tiles;
+  p.half_boxes = 0;
+  int rc;
+  CUtensorMap ma, mb0, mb1;
+  if ((rc = encode_map(&ma, a, p.M, p.K, lda, 128))) return rc;
+  if ((rc = encode_map(&mb0, b0, b_rows, p.K, ldb, 128))) return rc;
+  mb1 = mb0;
+  if (b1 != nullptr && (rc = encode_map(&mb1, b1, b_rows, p.K, ldb, 128))) return rc;
+  const int pairs = p.num_m_tiles * p.num_n_tiles;
+  const int clusters = std::max(1, std::min(pairs, effective_ctas(st) / 2));
+  gemm_pair_kernel<kMode, kOutF32><<<2 * clusters, kGemmThreads, kPairSmemBytes, stream>>>(ma, mb0, mb1, p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
+}
+
 int gateup_impl(DeviceState& st, const void* x, int64_t ldx, const void* w0, int64_t ldw,
                 const void* w_up, void* h, int64_t ldh, int64_t M, int64_t F, int64_t d,
                 int interleaved, cudaStream_t stream) {
@@ -312,6 +347,10 @@ int gateup_impl(DeviceState& st, const void* x, int64_t ldx, const void* w0, int
   p.group_m = pick_group_m(p.num_m_tiles, d);
   p.vec_ok = (aligned16(h) && ldh % 8 == 0) ? 1 : 0;
   p.status = st.status;
+  if (pair_enabled() && M > 128) {
+    return interleaved ? launch_gemm_pair<kGatedInterleaved, false>(st, x, ldx, w0, nullptr, ldw, 2 * F, p, stream)
+                       : launch_gemm_pair<kGatedSplit, false>(st, x, ldx, w0, w_up, ldw, F, p, stream);
+  }
   return interleaved ? launch_gemm<kGatedInterleaved, false>(st, ma, mb0, mb1, p, stream)
                      : launch_gemm<kGatedSplit, false>(st, ma, mb0, mb1, p, stream);
 }
@@ -342,6 +381,10 @@ int down_impl(DeviceState& st, const void* h, int64_t ldh, const void* w_down, i
   const bool f32 = out_dtype == FSWIGLU_OUT_F32;
   p.vec_ok = (aligned16(out) && ldo % (f32 ? 4 : 8) == 0) ? 1 : 0;
   p.status = st.status;
+  if (pair_enabled() && M > 128) {
+    return f32 ? launch_gemm_pair<kPlain, true>(st, h, ldh, w_down, nullptr, ldw, d, p, stream)
+               : launch_gemm_pair<kPlain, false>(st, h, ldh, w_down, nullptr, ldw, d, p, stream);
+  }
   return f32 ? launch_gemm<kPlain, true>(st, ma, mb, mb, p, stream)
              : launch_gemm<kPlain, false>(st, ma, mb, mb, p, stream);
 }
