@@ -279,10 +279,19 @@ int launch_gemm(const DeviceState& st, const CUtensorMap& ma, const CUtensorMap&
   return cudaGetLastError() == cudaSuccess ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
 }
 
-// Two-SM kernel (gemm_pair_sm100.cuh): experimental, selected with FSWIGLU_PAIR=1 for M > 128.
+// Two-SM kernel (gemm_pair_sm100.cuh): used whenever the problem fills at least one wave of 256-row
+// pair tiles (otherwise the one-SM kernel with its adaptive tile width spreads the work better).
+// Measured against the one-SM kernel at the 7B / 70B-shard shapes: bit-identical results, +10 ... +20 %
+// in short bursts (1647 vs 1502 TF/s gate-up), +1 % once the 1 kW power cap sets the clock.
+// FSWIGLU_PAIR=0 selects the one-SM kernel everywhere.
 bool pair_enabled() {
   const char* env = std::getenv("FSWIGLU_PAIR");
-  return env != nullptr && env[0] == '1';
+  return env == nullptr || env[0] != '0';
+}
+bool use_pair_kernel(const DeviceState& st, int64_t M, int64_t n_out, int tile_n) {
+  if (!pair_enabled() || M <= 128) return false;
+  const int64_t pairs = ((M + 255) / 256) * ((n_out + tile_n - 1) / tile_n);
+  return pairs >= effective_ctas(st) / 2;
 }
 
 // `p` arrives filled for the one-SM kernel; re-plan it for 256-row pair tiles of full width.
@@ -347,7 +356,7 @@ int gateup_impl(DeviceState& st, const void* x, int64_t ldx, const void* w0, int
   p.group_m = pick_group_m(p.num_m_tiles, d);
   p.vec_ok = (aligned16(h) && ldh % 8 == 0) ? 1 : 0;
   p.status = st.status;
-  if (pair_enabled() && M > 128) {
+  if (use_pair_kernel(st, M, F, 128)) {
     return interleaved ? launch_gemm_pair<kGatedInterleaved, false>(st, x, ldx, w0, nullptr, ldw, 2 * F, p, stream)
                        : launch_gemm_pair<kGatedSplit, false>(st, x, ldx, w0, w_up, ldw, F, p, stream);
   }
@@ -381,7 +390,7 @@ int down_impl(DeviceState& st, const void* h, int64_t ldh, const void* w_down, i
   const bool f32 = out_dtype == FSWIGLU_OUT_F32;
   p.vec_ok = (aligned16(out) && ldo % (f32 ? 4 : 8) == 0) ? 1 : 0;
   p.status = st.status;
-  if (pair_enabled() && M > 128) {
+  if (use_pair_kernel(st, M, d, 256)) {
     return f32 ? launch_gemm_pair<kPlain, true>(st, h, ldh, w_down, nullptr, ldw, d, p, stream)
                : launch_gemm_pair<kPlain, false>(st, h, ldh, w_down, nullptr, ldw, d, p, stream);
   }
@@ -654,6 +663,9 @@ int static_state(StaticState** out) {
     e = e ? e : opt_in_smem(gemm_tcgen05_kernel<kPlain, false>, kGemmSmemBytes);
     e = e ? e : opt_in_smem(gemm_tcgen05_kernel<kPlain, true>, kGemmSmemBytes);
     e = e ? e : opt_in_smem(gemm_tcgen05_kernel<kGatedSplit, false>, kGemmSmemBytes);
+    e = e ? e : opt_in_smem(gemm_pair_kernel<kPlain, false>, kPairSmemBytes);
+    e = e ? e : opt_in_smem(gemm_pair_kernel<kPlain, true>, kPairSmemBytes);
+    e = e ? e : opt_in_smem(gemm_pair_kernel<kGatedSplit, false>, kPairSmemBytes);
     if (e != cudaSuccess) return FSWIGLU_ERR_CUDA;
     st.base = static_cast<unsigned char*>(ptr);
     st.dev.num_sms = prop.multiProcessorCount;

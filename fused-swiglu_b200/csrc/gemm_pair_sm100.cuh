@@ -5,7 +5,7 @@
 // multicast loads are involved: every TMA load is an ordinary per-CTA load.
 //
 //   rank 0 ("leader")  warp 0 producer, warp 1 MMA issuer for BOTH CTAs, warps 2-5 epilogue
-//   rank 1 ("partner") warp 0 producer, warp 1 relays "my stage is loaded" to the leader,
+//   rank 1 ("partner") warp 0 producer (its loads count their bytes on the LEADER's stage barrier),
 //                      warps 2-5 epilogue (its own 128 rows, from its own TMEM)
 //
 // What the B half of a CTA holds (N = MMA columns, half of them per CTA, leader first):
@@ -122,9 +122,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             break;
           }
           const uint32_t a_dst = smem_base + stage * kPairStageBytes;
-          mbar_arrive_expect_tx(full_bar(stage), stage_tx_bytes);
-          tma_load_2d(a_dst, &map_a, full_bar(stage), kb * kBlockK, m0);
-          tma_load_2d(a_dst + kATileBytes, bmap, full_bar(stage), kb * kBlockK, b_row);
+          // one barrier per stage, in the leader: it expects the bytes of both CTAs' halves
+          if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2u * stage_tx_bytes);
+          const uint32_t leader_full = map_to_cta(full_bar(stage), 0);
+          tma_load_2d_pair(a_dst, &map_a, leader_full, kb * kBlockK, m0);
+          tma_load_2d_pair(a_dst + kATileBytes, bmap, leader_full, kb * kBlockK, b_row);
           issued_mask |= 1u << stage;
           last_parity_mask = (last_parity_mask & ~(1u << stage)) | (phase << stage);
           if (++stage == kPairStages) {
@@ -134,40 +136,29 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
       }
       if (wd.aborted()) {
-        for (int s = 0; s < kPairStages; ++s) {
-          if (issued_mask & (1u << s)) {
-            const uint32_t par = (last_parity_mask >> s) & 1u;
-            const unsigned long long t0 = global_timer_ns();
-            while (!mbar_try_wait(full_bar(s), par)) {
-              if (global_timer_ns() - t0 > 50000000ull) {
-                wd.give_up(kSiteDrainTma);
-                break;
+        if (rank == 0) {
+          for (int s = 0; s < kPairStages; ++s) {
+            if (issued_mask & (1u << s)) {
+              const uint32_t par = (last_parity_mask >> s) & 1u;
+              const unsigned long long t0 = global_timer_ns();
+              while (!mbar_try_wait(full_bar(s), par)) {
+                if (global_timer_ns() - t0 > 50000000ull) {
+                  wd.give_up(kSiteDrainTma);
+                  break;
+                }
               }
             }
+          }
+        } else {
+          // the partner's copies are counted in the leader: give them time to land before unwinding
+          const unsigned long long t0 = global_timer_ns();
+          while (global_timer_ns() - t0 < 100000ull) {
           }
         }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && rank == 1) {
-      // ---------------- partner: tell the leader when this CTA's half of a stage has landed ----------------
-      int stage = 0;
-      uint32_t phase = 0;
-      bool alive = true;
-      for (int tile = cluster_id; tile < num_tiles && alive; tile += num_clusters) {
-        for (int kb = 0; kb < num_kb; ++kb) {
-          if (!wd.wait(full_bar(stage), phase, kSitePeer)) {
-            alive = false;
-            break;
-          }
-          mbar_arrive_cluster(map_to_cta(peer_full_bar(stage), 0));
-          if (++stage == kPairStages) {
-            stage = 0;
-            phase ^= 1u;
-          }
-        }
-      }
-    } else if (lane == 0) {
+    if (lane == 0 && rank == 0) {
       // ------------------------------- leader: MMA issuer for the pair -------------------------------
       const uint32_t idesc = umma_idesc_bf16_f32(256, mma_n);
       int stage = 0;
@@ -180,8 +171,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kUmmaN);
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!wd.wait(full_bar(stage), phase, kSiteMmaFull) ||
-              !wd.wait<true>(peer_full_bar(stage), phase, kSitePeer)) {
+          if (!wd.wait<true>(full_bar(stage), phase, kSiteMmaFull)) {
             alive = false;
             break;
           }

@@ -165,6 +165,18 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap
       : "memory");
 }
 
+// Pair variant (two CTAs driving one cta_group::2 MMA): the box lands in THIS CTA's shared memory but
+// its bytes are counted on `cluster_bar`, a shared::cluster address that may name the leader CTA's
+// barrier (from mapa), so the leader needs no relay to learn that its partner's half has arrived.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst_smem, const CUtensorMap* map, uint32_t cluster_bar,
+                                                 int32_t x, int32_t y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(x), "r"(y)
+      : "memory");
+}
+
 // Same, with an L2 eviction-priority hint.
 __device__ __forceinline__ void tma_load_2d_hint(uint32_t dst_smem, const CUtensorMap* map,
                                                  uint32_t bar, int32_t x, int32_t y,
