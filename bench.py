@@ -391,7 +391,7 @@ def run_ours(args, rank, local_rank, world):
                         "frac_of_nominal_8000": hbm_achieved / NOMINAL_HBM_GBS, "bytes_per_launch": algo_bytes,
                         "ms_per_launch": gateup_ms, "launches_timed": len(gateup_events)}
         else:
-            roofline = {"bound": "tensor", "kernel": "gemm_tcgen05_kernel<gated-split> (gate-up + SiLU*up)",
+            roofline = {"bound": "tensor", "kernel": "gemm_pair_kernel<gated-split> (gate-up + SiLU*up, two-SM tcgen05)",
                         "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
                         "traffic": traffic, "peak_source": f"{peak_src} {'sustained' if long_region else 'burst'}",
                         "flops_per_launch": gateup_flops, "ms_per_launch": gateup_ms,
