@@ -54,9 +54,9 @@ NOMINAL_HBM_GBS = 8000.0
 NOMINAL_BF16_TFLOPS = 2250.0
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from `ncu --set full`
-# captures of one launch at the full workload size (gate-up GEMM at the 7B prefill shape; small-batch
+# captures of one launch at the full workload size (two-SM gate-up GEMM at the 7B prefill shape; small-batch
 # kernel at M = 16; the other small-batch sizes stream the same weights).
-NCU_TRAFFIC_BYTES = {"c2_llama2_7b_prefill": 217.62e6 + 81.37e6, "c4_llama3_70b_prefill": None,
+NCU_TRAFFIC_BYTES = {"c2_llama2_7b_prefill": 238.52e6 + 82.92e6, "c4_llama3_70b_prefill": None,
                      "c3_llama3_8b_decode_m16": 353.64e6 + 3.78e6}
 
 
