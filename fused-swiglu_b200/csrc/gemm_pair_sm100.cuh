@@ -13,8 +13,8 @@
 //   kGatedSplit        leader: tile_n rows of W_gate; partner: tile_n rows of W_up
 //   kGatedInterleaved  rows [2 n0 + rank * tile_n, +tile_n) of the packed W1W3
 // so the accumulator columns mean the same as in the one-SM kernel and the epilogue is shared.
-//
-// Status: compiled, selected only with FSWIGLU_PAIR=1.
+// Results are bit-identical to the one-SM kernel; the host selects this kernel when the problem
+// fills at least one wave of pair tiles.
 #pragma once
 
 #include "gemm_sm100.cuh"
@@ -42,7 +42,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_base + kPairStages * kPairStageBytes;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto peer_full_bar = [&](int s) { return bar_base + 8u * (kPairStages + s); };
   auto empty_bar = [&](int s) { return bar_base + 8u * (2 * kPairStages + s); };
   auto tfull_bar = [&](int a) { return bar_base + 8u * (3 * kPairStages + a); };
   auto tempty_bar = [&](int a) { return bar_base + 8u * (3 * kPairStages + 2 + a); };
@@ -60,7 +59,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   if (threadIdx.x == 0) {
     for (int s = 0; s < kPairStages; ++s) {
       mbar_init(full_bar(s), 1);
-      mbar_init(peer_full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
