@@ -748,6 +748,9 @@ int fswiglu_down_scatter_bf16(const void* h, int64_t ldh, const void* w_down, in
   p.scatter_world = world;
   p.scatter_rank = rank;
   p.rows_per_owner = static_cast<int>(rows_per_owner);
+  if (use_pair_kernel(*st, M, d, 256)) {
+    return launch_gemm_pair<kPlain, false>(*st, h, ldh, w_down, nullptr, ldw, d, p, static_cast<cudaStream_t>(stream));
+  }
   plan_tail_split(&p, effective_ctas(*st));
   CUtensorMap ma, mb;
   if ((rc = encode_map(&ma, h, M, F, ldh, 128))) return rc;

@@ -322,14 +322,16 @@ def test_launches_are_counted(fsw, cuda_dev):
     healthy(fsw)
 
 
-def test_push_reduction_kernels_on_one_gpu(fsw, cuda_dev):
+@pytest.mark.parametrize("world,M,d,F", [(4, 520, 264, 1096), (2, 2048, 2560, 528)])
+def test_push_reduction_kernels_on_one_gpu(fsw, cuda_dev, world, M, d, F):
     """The tensor-parallel 'push' kernels with all ranks emulated on ONE device, one after the other
     (no kernel waits for another): every rank's down GEMM scatters its bf16 partial rows into the
     owners' receive buffers, then every owner reduces its rows in fp32 and stores the result into
     all outputs.  Checked against the fp32 expression and for identical outputs on all 'ranks'."""
     import ctypes
     lib, capi = fsw.capi.lib, fsw.capi
-    world, M, d, F = 4, 520, 264, 1096          # ragged: 520 rows -> 130 per owner, F/4 = 274 -> 280/280/280/256
+    # case 1 is ragged (130 rows per owner, shards of 280/280/280/256 hidden units, one-SM kernel);
+    # case 2 is large enough (80 pair tiles) for the two-SM kernel to run the scatter epilogue
     x, wg, wu, wd = fsw.inputs.make_mlp_inputs(M, d, F, seed=12)
     rpo = (M + world - 1) // world
     xd = x.to(cuda_dev)
