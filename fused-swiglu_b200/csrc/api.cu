@@ -339,6 +339,12 @@ int gateup_impl(DeviceState& st, const void* x, int64_t ldx, const void* w0, int
   p.M = static_cast<int>(M);
   p.n_out = static_cast<int>(F);
   p.K = static_cast<int>(d);
+  p.vec_ok = (aligned16(h) && ldh % 8 == 0) ? 1 : 0;
+  p.status = st.status;
+  if (use_pair_kernel(st, M, F, 128)) {
+    return interleaved ? launch_gemm_pair<kGatedInterleaved, false>(st, x, ldx, w0, nullptr, ldw, 2 * F, p, stream)
+                       : launch_gemm_pair<kGatedSplit, false>(st, x, ldx, w0, w_up, ldw, F, p, stream);
+  }
   p.num_m_tiles = static_cast<int>((M + 127) / 128);
   p.tile_n = pick_tile_n(p.num_m_tiles, F, 128, 2, effective_ctas(st));
   p.num_n_tiles = static_cast<int>((F + p.tile_n - 1) / p.tile_n);
@@ -354,12 +360,6 @@ int gateup_impl(DeviceState& st, const void* x, int64_t ldx, const void* w0, int
     if ((rc = encode_map(&mb1, w_up, F, d, ldw, box_cols))) return rc;
   }
   p.group_m = pick_group_m(p.num_m_tiles, d);
-  p.vec_ok = (aligned16(h) && ldh % 8 == 0) ? 1 : 0;
-  p.status = st.status;
-  if (use_pair_kernel(st, M, F, 128)) {
-    return interleaved ? launch_gemm_pair<kGatedInterleaved, false>(st, x, ldx, w0, nullptr, ldw, 2 * F, p, stream)
-                       : launch_gemm_pair<kGatedSplit, false>(st, x, ldx, w0, w_up, ldw, F, p, stream);
-  }
   return interleaved ? launch_gemm<kGatedInterleaved, false>(st, ma, mb0, mb1, p, stream)
                      : launch_gemm<kGatedSplit, false>(st, ma, mb0, mb1, p, stream);
 }
@@ -379,6 +379,13 @@ int down_impl(DeviceState& st, const void* h, int64_t ldh, const void* w_down, i
   p.M = static_cast<int>(M);
   p.n_out = static_cast<int>(d);
   p.K = static_cast<int>(F);
+  const bool f32 = out_dtype == FSWIGLU_OUT_F32;
+  p.vec_ok = (aligned16(out) && ldo % (f32 ? 4 : 8) == 0) ? 1 : 0;
+  p.status = st.status;
+  if (use_pair_kernel(st, M, d, 256)) {
+    return f32 ? launch_gemm_pair<kPlain, true>(st, h, ldh, w_down, nullptr, ldw, d, p, stream)
+               : launch_gemm_pair<kPlain, false>(st, h, ldh, w_down, nullptr, ldw, d, p, stream);
+  }
   p.num_m_tiles = static_cast<int>((M + 127) / 128);
   p.tile_n = pick_tile_n(p.num_m_tiles, d, 256, 1, effective_ctas(st));
   p.num_n_tiles = static_cast<int>((d + p.tile_n - 1) / p.tile_n);
@@ -387,22 +394,15 @@ int down_impl(DeviceState& st, const void* h, int64_t ldh, const void* w_down, i
   if ((rc = encode_map(&ma, h, M, F, ldh, 128))) return rc;
   if ((rc = encode_map(&mb, w_down, d, F, ldw, p.half_boxes ? p.tile_n / 2 : p.tile_n))) return rc;
   p.group_m = pick_group_m(p.num_m_tiles, F);
-  const bool f32 = out_dtype == FSWIGLU_OUT_F32;
-  p.vec_ok = (aligned16(out) && ldo % (f32 ? 4 : 8) == 0) ? 1 : 0;
-  p.status = st.status;
-  if (use_pair_kernel(st, M, d, 256)) {
-    return f32 ? launch_gemm_pair<kPlain, true>(st, h, ldh, w_down, nullptr, ldw, d, p, stream)
-               : launch_gemm_pair<kPlain, false>(st, h, ldh, w_down, nullptr, ldw, d, p, stream);
-  }
   return f32 ? launch_gemm<kPlain, true>(st, ma, mb, mb, p, stream)
              : launch_gemm<kPlain, false>(st, ma, mb, mb, p, stream);
 }
 
 size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// Small-batch MLP: one cooperative weight-streaming launch (gate-up, hand-over, down) plus a
-// 4-byte memset of the hand-over counter.  `h` receives the bf16 hidden activations, `scratch`
-// holds the counter (decode_workspace_bytes).
+// Small-batch MLP: one cooperative weight-streaming launch (gate-up, hand-over, down) plus a small
+// memset of the hand-over and per-row-block arrival counters.  `h` receives the bf16 hidden
+// activations, `scratch` holds the counters and the fp32 partial tiles (decode_workspace_bytes).
 int decode_impl(DeviceState& st, const void* x, int64_t ldx, const void* w_gate, const void* w_up, int64_t ldw_gu,
                 const void* w_down, int64_t ldw_d, void* out, int64_t ldo, int out_dtype, int64_t M, int64_t d,
                 int64_t F, void* h, void* scratch, cudaStream_t stream) {
