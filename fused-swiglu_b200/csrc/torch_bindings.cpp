@@ -115,6 +115,25 @@ at::Tensor fused_swiglu_mlp_bf16(at::Tensor const& x, at::Tensor const& W_gate, 
   return out;
 }
 
+// Shape-only ("Meta") implementations: what fake-tensor tracing (torch.compile, export) needs to see
+// through the ops without running them.  The reference registers CUDA kernels only
+// (csrc/torch_bindings.cpp:45-50 there), so its ops cannot be traced.
+at::Tensor fused_swiglu_bf16_meta(at::Tensor const& X, at::Tensor const& W1W3) {
+  return at::empty({X.size(0), W1W3.size(0) / 2}, X.options());
+}
+void swiglu_fwd_bf16_meta(int64_t, int64_t, int64_t, at::Tensor const&, int64_t, at::Tensor const&, int64_t,
+                          at::Tensor const&, int64_t) {}
+at::Tensor fused_swiglu_gateup_bf16_meta(at::Tensor const& x, at::Tensor const& W_gate, at::Tensor const&) {
+  return at::empty({x.size(0), W_gate.size(0)}, x.options());
+}
+at::Tensor swiglu_down_bf16_meta(at::Tensor const& h, at::Tensor const& W_down, bool fp32_out) {
+  return at::empty({h.size(0), W_down.size(0)}, h.options().dtype(fp32_out ? at::kFloat : at::kBFloat16));
+}
+at::Tensor fused_swiglu_mlp_bf16_meta(at::Tensor const& x, at::Tensor const&, at::Tensor const&,
+                                      at::Tensor const& W_down) {
+  return at::empty({x.size(0), W_down.size(0)}, x.options());
+}
+
 namespace Fused_MLP {
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -140,6 +159,14 @@ TORCH_LIBRARY_IMPL(ASMLLM, CUDA, m) {
   m.impl("fused_swiglu_gateup_bf16", &fused_swiglu_gateup_bf16);
   m.impl("swiglu_down_bf16", &swiglu_down_bf16);
   m.impl("fused_swiglu_mlp_bf16", &fused_swiglu_mlp_bf16);
+}
+
+TORCH_LIBRARY_IMPL(ASMLLM, Meta, m) {
+  m.impl("fused_swiglu_bf16", &fused_swiglu_bf16_meta);
+  m.impl("swiglu_fwd_bf16", &swiglu_fwd_bf16_meta);
+  m.impl("fused_swiglu_gateup_bf16", &fused_swiglu_gateup_bf16_meta);
+  m.impl("swiglu_down_bf16", &swiglu_down_bf16_meta);
+  m.impl("fused_swiglu_mlp_bf16", &fused_swiglu_mlp_bf16_meta);
 }
 
 }  // namespace Fused_MLP

@@ -6,6 +6,7 @@
     pack    interleaved <-> split weight layouts, tensor-parallel shards
     tp      Megatron-style tensor-parallel forward (one process per GPU, NCCL)
     inputs  seeded synthetic inputs of the benchmark configurations
+    module  nn.Module wrapper (gate_proj / up_proj / down_proj) over the dispatcher op
 
 Importing the package loads the CUDA library and raises if it has not been built.
 """

@@ -174,3 +174,26 @@ def test_torch_extension_surface_loads_without_a_gpu():
     with pytest.raises(RuntimeError):
         fused_mlp_module.fused_swiglu_bf16(torch.zeros((4, 8), dtype=torch.bfloat16),
                                            torch.zeros((8, 8), dtype=torch.bfloat16))
+
+
+def test_meta_implementations_and_module_shapes():
+    """Shape-only dispatch (what fake-tensor tracing uses) and the nn.Module wrapper, on the meta device."""
+    import fused_mlp_module  # noqa: F401
+    from fused_swiglu_b200.module import FusedSwiGLUMLP
+
+    bf = dict(dtype=torch.bfloat16, device="meta")
+    x, wg, wd = torch.empty((12, 64), **bf), torch.empty((40, 64), **bf), torch.empty((64, 40), **bf)
+    ops = torch.ops.ASMLLM
+    assert ops.fused_swiglu_mlp_bf16(x, wg, wg, wd).shape == (12, 64)
+    assert ops.fused_swiglu_gateup_bf16(x, wg, wg).shape == (12, 40)
+    assert ops.fused_swiglu_bf16(x, torch.empty((80, 64), **bf)).shape == (12, 40)
+    assert ops.swiglu_down_bf16(torch.empty((12, 40), **bf), wd, True).dtype == torch.float32
+    assert ops.swiglu_fwd_bf16(12, 80, 64, x, 64, torch.empty((80, 64), **bf), 64, torch.empty((12, 80), **bf), 80) is None
+    mlp = FusedSwiGLUMLP(64, 40, device="meta")
+    assert mlp(torch.empty((2, 3, 64), **bf)).shape == (2, 3, 64)
+    assert [n for n, _ in mlp.named_parameters()] == ["gate_proj", "up_proj", "down_proj"]
+    with pytest.raises(ValueError):
+        FusedSwiGLUMLP(60, 40)
+    lin = torch.nn.Linear(64, 40, bias=False)
+    m2 = FusedSwiGLUMLP.from_linears(lin, torch.nn.Linear(64, 40, bias=False), torch.nn.Linear(40, 64, bias=False))
+    assert m2.gate_proj.dtype == torch.bfloat16 and torch.equal(m2.gate_proj.float(), lin.weight.to(torch.bfloat16).float())

@@ -84,3 +84,19 @@ def test_dtype_errors_are_runtime_errors(mod, cuda_dev):
         mod.fused_swiglu_bf16(A, A)
     with pytest.raises(RuntimeError):
         mod.fused_swiglu_bf16(A.bfloat16().cpu(), A.bfloat16().cpu())
+
+
+def test_module_wrapper_matches_the_op(mod, cuda_dev):
+    import fused_swiglu_b200 as fsw
+    from fused_swiglu_b200.module import FusedSwiGLUMLP
+
+    x, wg, wu, wd = (t.to(cuda_dev) for t in fsw.inputs.make_mlp_inputs(6 * 50, 256, 520, seed=21))
+    mlp = FusedSwiGLUMLP(256, 520, device=cuda_dev)
+    with torch.no_grad():
+        mlp.gate_proj.copy_(wg)
+        mlp.up_proj.copy_(wu)
+        mlp.down_proj.copy_(wd)
+    got = mlp(x.view(6, 50, 256))
+    want = mod.fused_swiglu_mlp_bf16(x, wg, wu, wd)
+    assert got.shape == (6, 50, 256) and torch.equal(got.reshape(-1, 256), want)
+    assert fsw.capi.device_status() == 0
