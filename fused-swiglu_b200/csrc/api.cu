@@ -45,14 +45,17 @@ __global__ void __launch_bounds__(256) cast_f32_to_bf16_kernel(const float4* __r
 // partial copy of them per source rank ([world][rows][cols], local memory, written by the ranks'
 // down-GEMM epilogues).  Sum the copies in fp32 in rank order (every element is reduced by exactly one
 // rank, so all ranks end up with identical bits), round once, and store the result into every
-// rank's output buffer (peer stores over NVLink).  16 bytes per thread per step.
+// rank's output buffer (peer stores over NVLink).  16 bytes per thread per step.  128 threads and no
+// shared memory per CTA, so that these CTAs fit on an SM next to a persistent GEMM CTA (registers:
+// 192 x 240 + 128 x 80 < 64 K) and the reduction of one row slab can run under the next slab's GEMMs
+// without SMs being set aside for it.
 struct ReduceBcastParams {
   const uint4* recv;
   void* out[8];          // per destination rank: base of its [*, cols] output, already offset to these rows
   long long n16;         // rows * cols / 8
   int world;
 };
-__global__ void __launch_bounds__(256) reduce_bcast_bf16_kernel(const ReduceBcastParams p) {
+__global__ void __launch_bounds__(128) reduce_bcast_bf16_kernel(const ReduceBcastParams p) {
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < p.n16; i += stride) {
     float acc[8];
@@ -86,6 +89,33 @@ __global__ void __launch_bounds__(256) reduce_bcast_bf16_kernel(const ReduceBcas
   }
 }
 
+// Per-row RMSNorm statistic  scale[r] = rsqrt(mean(x[r, :]^2) + eps)  in fp32: one warp per row,
+// 16-byte loads, fixed reduction order.  The gate-up epilogue multiplies its fp32 accumulators by
+// this factor, which equals normalising x before the GEMM (the norm's weight vector is folded into
+// the columns of W_gate / W_up once, at load time).
+__global__ void __launch_bounds__(256) rms_scale_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int M,
+                                                         int d, float eps, float* __restrict__ scale) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < M; row += gridDim.x * warps_per_block) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<long long>(row) * ldx);
+    float ss = 0.0f;
+    for (int i = lane; i < d / 8; i += 32) {
+      const uint4 q = __ldg(src + i);
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float a = __uint_as_float(w[k] << 16), b = __uint_as_float(w[k] & 0xffff0000u);
+        ss = fmaf(a, a, ss);
+        ss = fmaf(b, b, ss);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) scale[row] = rsqrtf(ss / static_cast<float>(d) + eps);
+  }
+}
+
 }  // namespace fsw
 
 namespace {
@@ -100,6 +130,7 @@ struct DeviceState {
   bool ready = false;
   int num_sms = 0;
   uint32_t* status = nullptr;  // device memory, 64 words
+  int max_ctas = 0;            // upper bound on the CTAs of the tiled kernels on this device, 0 = every SM
   // Lazily created by the host-buffer entry point only.
   bool host_ready = false;
   cudaStream_t h2d_stream = nullptr;
@@ -107,12 +138,12 @@ struct DeviceState {
   cudaEvent_t ev_start = nullptr;
   cudaEvent_t ev_h2d[kMaxHostSlabs] = {};
   cudaEvent_t ev_done[kMaxHostSlabs] = {};
+  std::mutex host_mutex;  // serialises the host-buffer entry point per device
 };
 
 std::mutex g_mutex;
 DeviceState g_dev[kMaxDevices];
 std::atomic<uint64_t> g_launches{0};
-std::atomic<int> g_max_ctas{0};  // 0 = use every SM
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                    const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -125,7 +156,36 @@ cudaError_t opt_in_smem(Kernel k, int bytes) {
   return cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
 }
 
-// One-time per-device set-up: capability check, status block, shared-memory opt-in.
+// Capability check, driver entry point for tensor-map encoding and the kernels' shared-memory
+// opt-in for device `dev` (the current device).  Allocates nothing.  Caller holds g_mutex.
+int prepare_device(int dev, int* num_sms) {
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return FSWIGLU_ERR_NO_DEVICE;
+  if (prop.major != 10) return FSWIGLU_ERR_NO_DEVICE;
+  *num_sms = prop.multiProcessorCount;
+  if (g_encode == nullptr) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+        fn == nullptr) {
+      return FSWIGLU_ERR_CUDA;
+    }
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  cudaError_t e = cudaSuccess;
+  e = e ? e : opt_in_smem(gemm_tcgen05_kernel<kPlain, false>, kGemmSmemBytes);
+  e = e ? e : opt_in_smem(gemm_tcgen05_kernel<kPlain, true>, kGemmSmemBytes);
+  e = e ? e : opt_in_smem(gemm_tcgen05_kernel<kGatedSplit, false>, kGemmSmemBytes);
+  e = e ? e : opt_in_smem(gemm_tcgen05_kernel<kGatedInterleaved, false>, kGemmSmemBytes);
+  e = e ? e : decode_opt_in_smem();
+  e = e ? e : opt_in_smem(gemm_pair_kernel<kPlain, false>, kPairSmemBytes);
+  e = e ? e : opt_in_smem(gemm_pair_kernel<kPlain, true>, kPairSmemBytes);
+  e = e ? e : opt_in_smem(gemm_pair_kernel<kGatedSplit, false>, kPairSmemBytes);
+  e = e ? e : opt_in_smem(gemm_pair_kernel<kGatedInterleaved, false>, kPairSmemBytes);
+  return e == cudaSuccess ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
+}
+
+// One-time per-device set-up of the ordinary entry points: the above plus the 256-byte status block.
 int device_state(DeviceState** out) {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess) return FSWIGLU_ERR_NO_DEVICE;
@@ -133,33 +193,9 @@ int device_state(DeviceState** out) {
   std::lock_guard<std::mutex> lock(g_mutex);
   DeviceState& st = g_dev[dev];
   if (!st.ready) {
-    cudaDeviceProp prop;
-    if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return FSWIGLU_ERR_NO_DEVICE;
-    if (prop.major != 10) return FSWIGLU_ERR_NO_DEVICE;
-    st.num_sms = prop.multiProcessorCount;
-    if (g_encode == nullptr) {
-      void* fn = nullptr;
-      cudaDriverEntryPointQueryResult q;
-      if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) !=
-              cudaSuccess ||
-          fn == nullptr) {
-        return FSWIGLU_ERR_CUDA;
-      }
-      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
-    }
+    if (int rc = prepare_device(dev, &st.num_sms)) return rc;
     if (cudaMalloc(&st.status, 256) != cudaSuccess) return FSWIGLU_ERR_CUDA;
     if (cudaMemset(st.status, 0, 256) != cudaSuccess) return FSWIGLU_ERR_CUDA;
-    cudaError_t e = cudaSuccess;
-    e = e ? e : opt_in_smem(gemm_tcgen05_kernel<kPlain, false>, kGemmSmemBytes);
-    e = e ? e : opt_in_smem(gemm_tcgen05_kernel<kPlain, true>, kGemmSmemBytes);
-    e = e ? e : opt_in_smem(gemm_tcgen05_kernel<kGatedSplit, false>, kGemmSmemBytes);
-    e = e ? e : opt_in_smem(gemm_tcgen05_kernel<kGatedInterleaved, false>, kGemmSmemBytes);
-    e = e ? e : decode_opt_in_smem();
-    e = e ? e : opt_in_smem(gemm_pair_kernel<kPlain, false>, kPairSmemBytes);
-    e = e ? e : opt_in_smem(gemm_pair_kernel<kPlain, true>, kPairSmemBytes);
-    e = e ? e : opt_in_smem(gemm_pair_kernel<kGatedSplit, false>, kPairSmemBytes);
-    e = e ? e : opt_in_smem(gemm_pair_kernel<kGatedInterleaved, false>, kPairSmemBytes);
-    if (e != cudaSuccess) return FSWIGLU_ERR_CUDA;
     st.ready = true;
   }
   *out = &st;
@@ -263,7 +299,7 @@ void plan_tail_split(GemmParams* p, int ctas) {
 }
 
 int effective_ctas(const DeviceState& st) {
-  const int cap = g_max_ctas.load(std::memory_order_relaxed);
+  const int cap = st.max_ctas;
   return (cap > 0 && cap < st.num_sms) ? cap : st.num_sms;
 }
 
@@ -283,21 +319,77 @@ int launch_gemm(const DeviceState& st, const CUtensorMap& ma, const CUtensorMap&
 // pair tiles (otherwise the one-SM kernel with its adaptive tile width spreads the work better).
 // Measured against the one-SM kernel at the 7B / 70B-shard shapes: bit-identical results, +10 ... +20 %
 // in short bursts (1647 vs 1502 TF/s gate-up), +1 % once the 1 kW power cap sets the clock.
-// FSWIGLU_PAIR=0 selects the one-SM kernel everywhere.
-bool pair_enabled() {
+// FSWIGLU_PAIR=0 selects the one-SM kernel everywhere, FSWIGLU_PAIR=force the two-SM kernel
+// everywhere (tests use it to run small ragged problems through the kernel the large shapes take).
+int pair_mode() {  // 0 never, 1 automatic, 2 always
   const char* env = std::getenv("FSWIGLU_PAIR");
-  return env == nullptr || env[0] != '0';
+  if (env == nullptr || env[0] == '\0') return 1;
+  if (env[0] == '0') return 0;
+  return (env[0] == 'f' || env[0] == 'F') ? 2 : 1;
 }
 bool use_pair_kernel(const DeviceState& st, int64_t M, int64_t n_out, int tile_n) {
-  if (!pair_enabled() || M <= 128) return false;
+  const int mode = pair_mode();
+  if (mode == 0 || effective_ctas(st) < 2) return false;
+  if (mode == 2) return true;
+  if (M <= 128) return false;
   const int64_t pairs = ((M + 255) / 256) * ((n_out + tile_n - 1) / tile_n);
   return pairs >= effective_ctas(st) / 2;
+}
+
+// Scratch of the split last wave (GemmParams::tail_*): a counter block, then the fp32 partial blocks.
+// A launch uses blocks (cluster + tail tile) * 2 + rank with cluster < clusters and tail tile <
+// clusters, so 4 * clusters blocks of 128 KiB always suffice; sized for the 74 clusters of a B200.
+constexpr size_t kTailCounterBytes = 4096;
+constexpr int kTailMaxClusters = 74;
+constexpr size_t kTailScratchBytes =
+    kTailCounterBytes + static_cast<size_t>(4) * kTailMaxClusters * kTailBlockFloats * sizeof(float);
+
+struct Scratch {
+  void* ptr = nullptr;
+  size_t bytes = 0;
+  bool counters_clean = false;  // the caller has already zeroed the counter block on this stream
+};
+
+// FSWIGLU_TAIL_SPLITK=0 turns the split off, =force applies it whenever the last wave is partial
+// (tests use it to reach the shared-tile path with small problems).
+int tail_split_k_mode() {  // 0 off, 1 when it pays, 2 always
+  const char* env = std::getenv("FSWIGLU_TAIL_SPLITK");
+  if (env == nullptr || env[0] == '\0') return 1;
+  if (env[0] == '0') return 0;
+  return (env[0] == 'f' || env[0] == 'F') ? 2 : 1;
+}
+
+// Decide how the last, partly filled wave of pair tiles is processed (see gemm_pair_sm100.cuh).
+// Splitting pays when the wave would leave enough clusters idle: every shared tile costs a round
+// trip of its 256 KiB accumulator through L2 (a few microseconds), a k-block about a third of one.
+void plan_pair_tail(GemmParams* p, int clusters, int num_kb, const Scratch& scratch) {
+  const int tiles = p->num_m_tiles * p->num_n_tiles;
+  p->tail_first = tiles;
+  p->tail_len = 0;
+  p->tail_partials = nullptr;
+  p->tail_counters = nullptr;
+  const int mode = tail_split_k_mode();
+  if (mode == 0 || scratch.ptr == nullptr || scratch.bytes < kTailScratchBytes) return;
+  if (clusters > kTailMaxClusters || clusters < 2) return;
+  const int rem = tiles % clusters;
+  if (rem == 0) return;
+  const long long saved_kb = static_cast<long long>(clusters - rem) * num_kb / clusters;  // per cluster
+  if (mode == 1 && saved_kb < 24) return;
+  long long len = (static_cast<long long>(rem) * num_kb + clusters - 1) / clusters;
+  const long long min_len = (num_kb + kTailMaxSegments - 2) / (kTailMaxSegments - 1);
+  if (len < min_len) len = min_len;
+  if (mode == 1 && len < 4) len = 4;
+  if (len >= num_kb) return;  // nothing to share
+  p->tail_first = tiles - rem;
+  p->tail_len = static_cast<int>(len);
+  p->tail_counters = static_cast<unsigned int*>(scratch.ptr);
+  p->tail_partials = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch.ptr) + kTailCounterBytes);
 }
 
 // `p` arrives filled for the one-SM kernel; re-plan it for 256-row pair tiles of full width.
 template <int kMode, bool kOutF32>
 int launch_gemm_pair(const DeviceState& st, const void* a, int64_t lda, const void* b0, const void* b1, int64_t ldb,
-                     int64_t b_rows, GemmParams p, cudaStream_t stream) {
+                     int64_t b_rows, GemmParams p, const Scratch& scratch, cudaStream_t stream) {
   p.tile_n = (kMode == kPlain) ? 256 : 128;
   p.num_m_tiles = (p.M + 255) / 256;
   p.num_n_tiles = (p.n_out + p.tile_n - 1) / p.tile_n;
@@ -313,6 +405,10 @@ int launch_gemm_pair(const DeviceState& st, const void* a, int64_t lda, const vo
   if (b1 != nullptr && (rc = encode_map(&mb1, b1, b_rows, p.K, ldb, 128))) return rc;
   const int pairs = p.num_m_tiles * p.num_n_tiles;
   const int clusters = std::max(1, std::min(pairs, effective_ctas(st) / 2));
+  plan_pair_tail(&p, clusters, (p.K + kBlockK - 1) / kBlockK, scratch);
+  if (p.tail_len > 0 && !scratch.counters_clean) {
+    if (cudaMemsetAsync(p.tail_counters, 0, kTailCounterBytes, stream) != cudaSuccess) return FSWIGLU_ERR_CUDA;
+  }
   gemm_pair_kernel<kMode, kOutF32><<<2 * clusters, kGemmThreads, kPairSmemBytes, stream>>>(ma, mb0, mb1, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError() == cudaSuccess ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
@@ -320,7 +416,7 @@ int launch_gemm_pair(const DeviceState& st, const void* a, int64_t lda, const vo
 
 int gateup_impl(DeviceState& st, const void* x, int64_t ldx, const void* w0, int64_t ldw,
                 const void* w_up, void* h, int64_t ldh, int64_t M, int64_t F, int64_t d,
-                int interleaved, cudaStream_t stream) {
+                int interleaved, const float* row_scale, const Scratch& scratch, cudaStream_t stream) {
   int rc;
   if (M == 0) return FSWIGLU_OK;  // empty batch: nothing to read or write, pointers may be null
   if ((rc = check_matrix(x, M, d, ldx, true))) return rc;
@@ -332,6 +428,7 @@ int gateup_impl(DeviceState& st, const void* x, int64_t ldx, const void* w0, int
     if ((rc = check_matrix(w_up, F, d, ldw, true))) return rc;
   }
   if ((rc = check_matrix(h, M, F, ldh, false))) return rc;
+  if (row_scale != nullptr && (reinterpret_cast<uintptr_t>(row_scale) & 3u) != 0) return FSWIGLU_ERR_ALIGNMENT;
 
   GemmParams p = {};
   p.out = h;
@@ -341,9 +438,11 @@ int gateup_impl(DeviceState& st, const void* x, int64_t ldx, const void* w0, int
   p.K = static_cast<int>(d);
   p.vec_ok = (aligned16(h) && ldh % 8 == 0) ? 1 : 0;
   p.status = st.status;
+  p.row_scale = row_scale;
   if (use_pair_kernel(st, M, F, 128)) {
-    return interleaved ? launch_gemm_pair<kGatedInterleaved, false>(st, x, ldx, w0, nullptr, ldw, 2 * F, p, stream)
-                       : launch_gemm_pair<kGatedSplit, false>(st, x, ldx, w0, w_up, ldw, F, p, stream);
+    return interleaved
+               ? launch_gemm_pair<kGatedInterleaved, false>(st, x, ldx, w0, nullptr, ldw, 2 * F, p, scratch, stream)
+               : launch_gemm_pair<kGatedSplit, false>(st, x, ldx, w0, w_up, ldw, F, p, scratch, stream);
   }
   p.num_m_tiles = static_cast<int>((M + 127) / 128);
   p.tile_n = pick_tile_n(p.num_m_tiles, F, 128, 2, effective_ctas(st));
@@ -364,14 +463,24 @@ int gateup_impl(DeviceState& st, const void* x, int64_t ldx, const void* w0, int
                      : launch_gemm<kGatedSplit, false>(st, ma, mb0, mb1, p, stream);
 }
 
+// The optional residual [M, d] (bf16) is read with 16-byte loads: aligned base, pitch and width.
+int check_residual(const void* residual, int64_t ldr, int64_t d) {
+  if (residual == nullptr) return FSWIGLU_OK;
+  if (ldr < d || d % 8 != 0) return FSWIGLU_ERR_SHAPE;
+  if (!aligned16(residual) || ldr % 8 != 0) return FSWIGLU_ERR_ALIGNMENT;
+  return FSWIGLU_OK;
+}
+
 int down_impl(DeviceState& st, const void* h, int64_t ldh, const void* w_down, int64_t ldw, void* out,
-              int64_t ldo, int64_t M, int64_t d, int64_t F, int out_dtype, cudaStream_t stream) {
+              int64_t ldo, int64_t M, int64_t d, int64_t F, int out_dtype, const void* residual, int64_t ldr,
+              const Scratch& scratch, cudaStream_t stream) {
   int rc;
   if (out_dtype != FSWIGLU_OUT_BF16 && out_dtype != FSWIGLU_OUT_F32) return FSWIGLU_ERR_BAD_ARG;
   if (M == 0) return FSWIGLU_OK;
   if ((rc = check_matrix(h, M, F, ldh, true))) return rc;
   if ((rc = check_matrix(w_down, d, F, ldw, true))) return rc;
   if ((rc = check_matrix(out, M, d, ldo, false))) return rc;
+  if ((rc = check_residual(residual, ldr, d))) return rc;
 
   GemmParams p = {};
   p.out = out;
@@ -382,9 +491,11 @@ int down_impl(DeviceState& st, const void* h, int64_t ldh, const void* w_down, i
   const bool f32 = out_dtype == FSWIGLU_OUT_F32;
   p.vec_ok = (aligned16(out) && ldo % (f32 ? 4 : 8) == 0) ? 1 : 0;
   p.status = st.status;
+  p.residual = residual;
+  p.ld_res = ldr;
   if (use_pair_kernel(st, M, d, 256)) {
-    return f32 ? launch_gemm_pair<kPlain, true>(st, h, ldh, w_down, nullptr, ldw, d, p, stream)
-               : launch_gemm_pair<kPlain, false>(st, h, ldh, w_down, nullptr, ldw, d, p, stream);
+    return f32 ? launch_gemm_pair<kPlain, true>(st, h, ldh, w_down, nullptr, ldw, d, p, scratch, stream)
+               : launch_gemm_pair<kPlain, false>(st, h, ldh, w_down, nullptr, ldw, d, p, scratch, stream);
   }
   p.num_m_tiles = static_cast<int>((M + 127) / 128);
   p.tile_n = pick_tile_n(p.num_m_tiles, d, 256, 1, effective_ctas(st));
@@ -403,9 +514,23 @@ size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 // Small-batch MLP: one cooperative weight-streaming launch (gate-up, hand-over, down) plus a small
 // memset of the hand-over and per-row-block arrival counters.  `h` receives the bf16 hidden
 // activations, `scratch` holds the counters and the fp32 partial tiles (decode_workspace_bytes).
+struct Fusions {
+  const float* row_scale = nullptr;  // [M] fp32, applied to gate and up before SiLU
+  const void* residual = nullptr;    // bf16 [M, d], added to the output in fp32
+  int64_t ld_res = 0;
+};
+
+int decode_prefetch_units() {
+  if (const char* env = std::getenv("FSWIGLU_DECODE_PREFETCH")) {
+    const int v = std::atoi(env);
+    if (v >= 0 && v <= 4096) return v;
+  }
+  return 24;  // 24 tiles x 16 KiB x 148 SMs = 57 MB ahead of the ring, well inside the L2
+}
+
 int decode_impl(DeviceState& st, const void* x, int64_t ldx, const void* w_gate, const void* w_up, int64_t ldw_gu,
                 const void* w_down, int64_t ldw_d, void* out, int64_t ldo, int out_dtype, int64_t M, int64_t d,
-                int64_t F, void* h, void* scratch, cudaStream_t stream) {
+                int64_t F, const Fusions& fu, void* h, void* scratch, cudaStream_t stream) {
   int rc;
   if (out_dtype != FSWIGLU_OUT_BF16 && out_dtype != FSWIGLU_OUT_F32) return FSWIGLU_ERR_BAD_ARG;
   if ((rc = check_matrix(x, M, d, ldx, true))) return rc;
@@ -413,6 +538,7 @@ int decode_impl(DeviceState& st, const void* x, int64_t ldx, const void* w_gate,
   if ((rc = check_matrix(w_up, F, d, ldw_gu, true))) return rc;
   if ((rc = check_matrix(w_down, d, F, ldw_d, true))) return rc;
   if ((rc = check_matrix(out, M, d, ldo, false))) return rc;
+  if ((rc = check_residual(fu.residual, fu.ld_res, d))) return rc;
 
   const int n_pad = decode_pad_tokens(M);
   const int rb2 = static_cast<int>((d + 127) / 128), kb2 = static_cast<int>((F + 63) / 64);
@@ -438,6 +564,10 @@ int decode_impl(DeviceState& st, const void* x, int64_t ldx, const void* w_gate,
   p.handover = counters;
   p.M = static_cast<int>(M);
   p.n_pad = n_pad;
+  p.prefetch_units = decode_prefetch_units();
+  p.row_scale = fu.row_scale;
+  p.residual = fu.residual;
+  p.ld_res = fu.ld_res;
   p.status = st.status;
 
   CUtensorMap m_gate, m_up, m_x, m_down, m_h;
@@ -461,11 +591,43 @@ int decode_impl(DeviceState& st, const void* x, int64_t ldx, const void* w_gate,
     // Not every CTA can be resident right now (SMs held by someone else): the hand-over inside the
     // kernel would not be safe, so the launch was refused.  The tiled kernels need no co-residency.
     (void)cudaGetLastError();
-    if ((rc = gateup_impl(st, x, ldx, w_gate, ldw_gu, w_up, h, F, M, F, d, 0, stream))) return rc;
-    return down_impl(st, h, F, w_down, ldw_d, out, ldo, M, d, F, out_dtype, stream);
+    if ((rc = gateup_impl(st, x, ldx, w_gate, ldw_gu, w_up, h, F, M, F, d, 0, fu.row_scale, Scratch{}, stream)))
+      return rc;
+    return down_impl(st, h, F, w_down, ldw_d, out, ldo, M, d, F, out_dtype, fu.residual, fu.ld_res, Scratch{},
+                     stream);
   }
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return e == cudaSuccess ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
+}
+
+// Workspace of the whole-MLP call: [h: M x F bf16][small-batch counters + partial tiles, M <= 64]
+// [scratch of the split last wave, M > 128], every part 256-byte aligned.
+size_t mlp_h_bytes(int64_t M, int64_t F) { return round_up(static_cast<size_t>(M) * static_cast<size_t>(F) * 2u, 256); }
+
+int mlp_impl(DeviceState& st, const void* x, int64_t ldx, const void* w_gate, const void* w_up, int64_t ldw_gu,
+             const void* w_down, int64_t ldw_d, void* out, int64_t ldo, int out_dtype, int64_t M, int64_t d,
+             int64_t F, const Fusions& fu, void* workspace, size_t workspace_bytes, cudaStream_t s) {
+  if (workspace == nullptr || workspace_bytes < fswiglu_workspace_bytes(M, d, F) ||
+      (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) {
+    return FSWIGLU_ERR_WORKSPACE;
+  }
+  void* h = workspace;
+  uint8_t* after_h = static_cast<uint8_t*>(workspace) + mlp_h_bytes(M, F);
+  if (M <= kDecodeMaxTokens && decode_supported(M, d, F, ldx, ldw_gu, ldw_d) &&
+      std::getenv("FSWIGLU_NO_DECODE_PATH") == nullptr) {
+    return decode_impl(st, x, ldx, w_gate, w_up, ldw_gu, w_down, ldw_d, out, ldo, out_dtype, M, d, F, fu, h, after_h,
+                       s);
+  }
+  Scratch scratch;
+  if (M > 128) {
+    scratch.ptr = after_h + (M <= kDecodeMaxTokens ? decode_workspace_bytes(M, d, F) : 0);
+    scratch.bytes = kTailScratchBytes;
+    // one memset serves both launches: each leaves the counters it used at zero
+    if (cudaMemsetAsync(scratch.ptr, 0, kTailCounterBytes, s) != cudaSuccess) return FSWIGLU_ERR_CUDA;
+    scratch.counters_clean = true;
+  }
+  if (int rc = gateup_impl(st, x, ldx, w_gate, ldw_gu, w_up, h, F, M, F, d, 0, fu.row_scale, scratch, s)) return rc;
+  return down_impl(st, h, F, w_down, ldw_d, out, ldo, M, d, F, out_dtype, fu.residual, fu.ld_res, scratch, s);
 }
 
 }  // namespace
@@ -475,26 +637,50 @@ extern "C" {
 int fswiglu_gateup_bf16(const void* x, int64_t ldx, const void* w_gate_or_w13, int64_t ldw,
                         const void* w_up, void* h, int64_t ldh, int64_t M, int64_t F, int64_t d,
                         int interleaved, void* stream) {
+  return fswiglu_gateup_bf16_ex(x, ldx, w_gate_or_w13, ldw, w_up, h, ldh, M, F, d, interleaved, nullptr, nullptr, 0,
+                                stream);
+}
+
+int fswiglu_gateup_bf16_ex(const void* x, int64_t ldx, const void* w_gate_or_w13, int64_t ldw, const void* w_up,
+                           void* h, int64_t ldh, int64_t M, int64_t F, int64_t d, int interleaved,
+                           const float* row_scale, void* scratch, size_t scratch_bytes, void* stream) {
   if (M < 0 || F <= 0 || d <= 0) return FSWIGLU_ERR_BAD_ARG;
   DeviceState* st = nullptr;
   if (int rc = device_state(&st)) return rc;
-  return gateup_impl(*st, x, ldx, w_gate_or_w13, ldw, w_up, h, ldh, M, F, d, interleaved,
+  Scratch sc;
+  if (scratch != nullptr && (reinterpret_cast<uintptr_t>(scratch) & 255u) != 0) return FSWIGLU_ERR_WORKSPACE;
+  sc.ptr = scratch;
+  sc.bytes = scratch_bytes;
+  return gateup_impl(*st, x, ldx, w_gate_or_w13, ldw, w_up, h, ldh, M, F, d, interleaved, row_scale, sc,
                      static_cast<cudaStream_t>(stream));
 }
 
 int fswiglu_down_bf16(const void* h, int64_t ldh, const void* w_down, int64_t ldw, void* out,
                       int64_t ldo, int64_t M, int64_t d, int64_t F, int out_dtype, void* stream) {
+  return fswiglu_down_bf16_ex(h, ldh, w_down, ldw, out, ldo, M, d, F, out_dtype, nullptr, 0, nullptr, 0, stream);
+}
+
+int fswiglu_down_bf16_ex(const void* h, int64_t ldh, const void* w_down, int64_t ldw, void* out, int64_t ldo,
+                         int64_t M, int64_t d, int64_t F, int out_dtype, const void* residual, int64_t ldr,
+                         void* scratch, size_t scratch_bytes, void* stream) {
   if (M < 0 || F <= 0 || d <= 0) return FSWIGLU_ERR_BAD_ARG;
   DeviceState* st = nullptr;
   if (int rc = device_state(&st)) return rc;
-  return down_impl(*st, h, ldh, w_down, ldw, out, ldo, M, d, F, out_dtype,
+  Scratch sc;
+  if (scratch != nullptr && (reinterpret_cast<uintptr_t>(scratch) & 255u) != 0) return FSWIGLU_ERR_WORKSPACE;
+  sc.ptr = scratch;
+  sc.bytes = scratch_bytes;
+  return down_impl(*st, h, ldh, w_down, ldw, out, ldo, M, d, F, out_dtype, residual, ldr, sc,
                    static_cast<cudaStream_t>(stream));
 }
 
+size_t fswiglu_gemm_scratch_bytes(void) { return kTailScratchBytes; }
+
 size_t fswiglu_workspace_bytes(int64_t M, int64_t d, int64_t F) {
   if (M <= 0 || d <= 0 || F <= 0) return 0;
-  size_t bytes = round_up(static_cast<size_t>(M) * static_cast<size_t>(F) * 2u, 256);
+  size_t bytes = mlp_h_bytes(M, F);
   if (M <= kDecodeMaxTokens) bytes += decode_workspace_bytes(M, d, F);
+  if (M > 128) bytes += kTailScratchBytes;
   return bytes;
 }
 
@@ -502,25 +688,38 @@ int fswiglu_mlp_bf16(const void* x, int64_t ldx, const void* w_gate, const void*
                      const void* w_down, int64_t ldw_d, void* out, int64_t ldo, int out_dtype,
                      int64_t M, int64_t d, int64_t F, void* workspace, size_t workspace_bytes,
                      void* stream) {
+  return fswiglu_mlp_bf16_ex(x, ldx, nullptr, w_gate, w_up, ldw_gu, w_down, ldw_d, nullptr, 0, out, ldo, out_dtype, M,
+                             d, F, workspace, workspace_bytes, stream);
+}
+
+int fswiglu_mlp_bf16_ex(const void* x, int64_t ldx, const float* row_scale, const void* w_gate, const void* w_up,
+                        int64_t ldw_gu, const void* w_down, int64_t ldw_d, const void* residual, int64_t ldr,
+                        void* out, int64_t ldo, int out_dtype, int64_t M, int64_t d, int64_t F, void* workspace,
+                        size_t workspace_bytes, void* stream) {
   if (M < 0 || F <= 0 || d <= 0) return FSWIGLU_ERR_BAD_ARG;
   if (M == 0) return FSWIGLU_OK;
   DeviceState* st = nullptr;
   if (int rc = device_state(&st)) return rc;
-  if (workspace == nullptr || workspace_bytes < fswiglu_workspace_bytes(M, d, F) ||
-      (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) {
-    return FSWIGLU_ERR_WORKSPACE;
-  }
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  void* h = workspace;
-  if (M <= kDecodeMaxTokens && decode_supported(M, d, F, ldx, ldw_gu, ldw_d) &&
-      std::getenv("FSWIGLU_NO_DECODE_PATH") == nullptr) {
-    void* scratch = static_cast<uint8_t*>(workspace) +
-                    round_up(static_cast<size_t>(M) * static_cast<size_t>(F) * 2u, 256);
-    return decode_impl(*st, x, ldx, w_gate, w_up, ldw_gu, w_down, ldw_d, out, ldo, out_dtype, M, d, F, h, scratch,
-                       s);
-  }
-  if (int rc = gateup_impl(*st, x, ldx, w_gate, ldw_gu, w_up, h, F, M, F, d, 0, s)) return rc;
-  return down_impl(*st, h, F, w_down, ldw_d, out, ldo, M, d, F, out_dtype, s);
+  Fusions fu;
+  fu.row_scale = row_scale;
+  fu.residual = residual;
+  fu.ld_res = ldr;
+  return mlp_impl(*st, x, ldx, w_gate, w_up, ldw_gu, w_down, ldw_d, out, ldo, out_dtype, M, d, F, fu, workspace,
+                  workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int fswiglu_rms_scale_f32(const void* x, int64_t ldx, int64_t M, int64_t d, float eps, float* scale, void* stream) {
+  if (M < 0 || d <= 0 || !(eps >= 0.0f)) return FSWIGLU_ERR_BAD_ARG;
+  if (M == 0) return FSWIGLU_OK;
+  if (int rc = check_matrix(x, M, d, ldx, true)) return rc;
+  if (scale == nullptr) return FSWIGLU_ERR_BAD_ARG;
+  DeviceState* st = nullptr;
+  if (int rc = device_state(&st)) return rc;
+  const long long blocks = std::min<long long>((M + 7) / 8, static_cast<long long>(st->num_sms) * 8);
+  rms_scale_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), ldx, static_cast<int>(M), static_cast<int>(d), eps, scale);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
 }
 
 namespace {
@@ -533,6 +732,16 @@ int64_t host_slab_rows(int64_t M) {
   if (rows < min_rows) rows = (min_rows + 127) / 128 * 128;
   if (rows > M) rows = M;
   return rows;
+}
+
+// Workspace of one slab's MLP call: the full slab and the ragged last slab may take different paths
+// (a last slab of <= 64 rows takes the small-batch kernel with its own partial tiles).
+size_t host_slab_workspace_bytes(int64_t M, int64_t d, int64_t F) {
+  const int64_t slab = host_slab_rows(M);
+  size_t bytes = fswiglu_workspace_bytes(slab, d, F);
+  const int64_t last = M % slab;
+  if (last != 0) bytes = std::max(bytes, fswiglu_workspace_bytes(last, d, F));
+  return round_up(bytes, 256);
 }
 
 int host_state(DeviceState& st) {
@@ -558,7 +767,7 @@ int host_state(DeviceState& st) {
 size_t fswiglu_host_workspace_bytes(int64_t M, int64_t d, int64_t F) {
   if (M <= 0 || d <= 0 || F <= 0) return 0;
   const size_t act = round_up(static_cast<size_t>(M) * static_cast<size_t>(d) * 2u, 256);
-  return 2 * act + round_up(fswiglu_workspace_bytes(host_slab_rows(M), d, F), 256);
+  return 2 * act + host_slab_workspace_bytes(M, d, F);
 }
 
 int fswiglu_mlp_bf16_host(const void* x_host, const void* w_gate, const void* w_up,
@@ -574,13 +783,15 @@ int fswiglu_mlp_bf16_host(const void* x_host, const void* w_gate, const void* w_
       (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) {
     return FSWIGLU_ERR_WORKSPACE;
   }
+  // The internal copy streams and events belong to the device: one host-buffer call per device at a time.
+  std::lock_guard<std::mutex> lock(st->host_mutex);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const size_t act = round_up(static_cast<size_t>(M) * static_cast<size_t>(d) * 2u, 256);
   uint8_t* x_dev = static_cast<uint8_t*>(workspace);
   uint8_t* out_dev = x_dev + act;
   uint8_t* mlp_ws = out_dev + act;
   const int64_t slab = host_slab_rows(M);
-  const size_t mlp_ws_bytes = fswiglu_workspace_bytes(slab, d, F);
+  const size_t mlp_ws_bytes = host_slab_workspace_bytes(M, d, F);
   const int num_slabs = static_cast<int>((M + slab - 1) / slab);
   const size_t row_bytes = static_cast<size_t>(d) * 2u;
 
@@ -645,35 +856,31 @@ int static_state(StaticState** out) {
   std::lock_guard<std::mutex> lock(g_mutex);
   StaticState& st = g_static[dev];
   if (!st.ready) {
-    cudaDeviceProp prop;
-    if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return FSWIGLU_ERR_NO_DEVICE;
-    if (prop.major != 10) return FSWIGLU_ERR_NO_DEVICE;
-    if (g_encode == nullptr) {
-      void* fn = nullptr;
-      cudaDriverEntryPointQueryResult q;
-      if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
-          fn == nullptr) {
-        return FSWIGLU_ERR_CUDA;
-      }
-      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
-    }
+    int num_sms = 0;
+    if (int rc = prepare_device(dev, &num_sms)) return rc;
     void* ptr = nullptr;
     if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) return FSWIGLU_ERR_CUDA;
-    cudaError_t e = cudaSuccess;
-    e = e ? e : opt_in_smem(gemm_tcgen05_kernel<kPlain, false>, kGemmSmemBytes);
-    e = e ? e : opt_in_smem(gemm_tcgen05_kernel<kPlain, true>, kGemmSmemBytes);
-    e = e ? e : opt_in_smem(gemm_tcgen05_kernel<kGatedSplit, false>, kGemmSmemBytes);
-    e = e ? e : opt_in_smem(gemm_pair_kernel<kPlain, false>, kPairSmemBytes);
-    e = e ? e : opt_in_smem(gemm_pair_kernel<kPlain, true>, kPairSmemBytes);
-    e = e ? e : opt_in_smem(gemm_pair_kernel<kGatedSplit, false>, kPairSmemBytes);
-    if (e != cudaSuccess) return FSWIGLU_ERR_CUDA;
     st.base = static_cast<unsigned char*>(ptr);
-    st.dev.num_sms = prop.multiProcessorCount;
+    st.dev.num_sms = num_sms;
     st.dev.status = reinterpret_cast<uint32_t*>(st.base);
     st.dev.ready = true;
     st.ready = true;
   }
   *out = &st;
+  return FSWIGLU_OK;
+}
+
+// Copy a watchdog word to the host and clear it if it was set.  No allocation.
+int read_and_clear_status(uint32_t* device_word, uint32_t* out, cudaStream_t s) {
+  uint32_t word = 0;
+  if (cudaMemcpyAsync(&word, device_word, sizeof(word), cudaMemcpyDeviceToHost, s) != cudaSuccess)
+    return FSWIGLU_ERR_CUDA;
+  if (cudaStreamSynchronize(s) != cudaSuccess) return FSWIGLU_ERR_CUDA;
+  if (word != 0) {
+    if (cudaMemsetAsync(device_word, 0, sizeof(word), s) != cudaSuccess) return FSWIGLU_ERR_CUDA;
+    if (cudaStreamSynchronize(s) != cudaSuccess) return FSWIGLU_ERR_CUDA;
+  }
+  *out = word;
   return FSWIGLU_OK;
 }
 
@@ -692,8 +899,17 @@ int fswiglu_mlp_bf16_static(const void* x, int64_t ldx, const void* w_gate, cons
   if (int rc = static_state(&st)) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   void* h = st->base + kStaticHeaderBytes;
-  if (int rc = gateup_impl(st->dev, x, ldx, w_gate, ldw_gu, w_up, h, F, M, F, d, 0, s)) return rc;
-  return down_impl(st->dev, h, F, w_down, ldw_d, out, ldo, M, d, F, out_dtype, s);
+  if (int rc = gateup_impl(st->dev, x, ldx, w_gate, ldw_gu, w_up, h, F, M, F, d, 0, nullptr, Scratch{}, s)) return rc;
+  return down_impl(st->dev, h, F, w_down, ldw_d, out, ldo, M, d, F, out_dtype, nullptr, 0, Scratch{}, s);
+}
+
+int fswiglu_static_status(uint32_t* status, void* stream) {
+  StaticState* st = nullptr;
+  if (int rc = static_state(&st)) return rc;
+  uint32_t word = 0;
+  if (int rc = read_and_clear_status(st->dev.status, &word, static_cast<cudaStream_t>(stream))) return rc;
+  if (status != nullptr) *status = word;
+  return word == 0 ? FSWIGLU_OK : FSWIGLU_ERR_WATCHDOG;
 }
 
 int fswiglu_cast_f32_to_bf16(const void* src, void* dst, int64_t n, void* stream) {
@@ -717,7 +933,7 @@ int fswiglu_cast_f32_to_bf16(const void* src, void* dst, int64_t n, void* stream
 
 int fswiglu_down_scatter_bf16(const void* h, int64_t ldh, const void* w_down, int64_t ldw,
                               void* const* recv_ptrs, int world, int rank, int64_t rows_per_owner, int64_t M,
-                              int64_t d, int64_t F, void* stream) {
+                              int64_t d, int64_t F, void* scratch, size_t scratch_bytes, void* stream) {
   if (M < 0 || F <= 0 || d <= 0 || world < 1 || world > 8 || rank < 0 || rank >= world || rows_per_owner <= 0 ||
       recv_ptrs == nullptr)
     return FSWIGLU_ERR_BAD_ARG;
@@ -749,7 +965,12 @@ int fswiglu_down_scatter_bf16(const void* h, int64_t ldh, const void* w_down, in
   p.scatter_rank = rank;
   p.rows_per_owner = static_cast<int>(rows_per_owner);
   if (use_pair_kernel(*st, M, d, 256)) {
-    return launch_gemm_pair<kPlain, false>(*st, h, ldh, w_down, nullptr, ldw, d, p, static_cast<cudaStream_t>(stream));
+    Scratch sc;
+    if (scratch != nullptr && (reinterpret_cast<uintptr_t>(scratch) & 255u) != 0) return FSWIGLU_ERR_WORKSPACE;
+    sc.ptr = scratch;
+    sc.bytes = scratch_bytes;
+    return launch_gemm_pair<kPlain, false>(*st, h, ldh, w_down, nullptr, ldw, d, p, sc,
+                                           static_cast<cudaStream_t>(stream));
   }
   plan_tail_split(&p, effective_ctas(*st));
   CUtensorMap ma, mb;
@@ -775,16 +996,21 @@ int fswiglu_reduce_bcast_bf16(const void* recv_local, void* const* out_ptrs, int
   }
   p.n16 = rows * cols / 8;
   p.world = world;
-  int ctas = max_ctas > 0 ? max_ctas : 32;
-  const long long need = (p.n16 + 255) / 256;
+  int ctas = max_ctas > 0 ? max_ctas : 64;
+  const long long need = (p.n16 + 127) / 128;
   if (ctas > need) ctas = static_cast<int>(need);
-  reduce_bcast_bf16_kernel<<<ctas, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  reduce_bcast_bf16_kernel<<<ctas, 128, 0, static_cast<cudaStream_t>(stream)>>>(p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError() == cudaSuccess ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
 }
 
 int fswiglu_set_max_ctas(int max_ctas) {
-  return g_max_ctas.exchange(max_ctas < 0 ? 0 : max_ctas, std::memory_order_relaxed);
+  DeviceState* st = nullptr;
+  if (int rc = device_state(&st)) return rc;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  const int prev = st->max_ctas;
+  st->max_ctas = max_ctas < 0 ? 0 : max_ctas;
+  return prev;
 }
 
 int fswiglu_device_status(uint32_t* status, void* stream) {
@@ -792,12 +1018,13 @@ int fswiglu_device_status(uint32_t* status, void* stream) {
   if (int rc = device_state(&st)) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   uint32_t word = 0;
-  if (cudaMemcpyAsync(&word, st->status, sizeof(word), cudaMemcpyDeviceToHost, s) != cudaSuccess)
-    return FSWIGLU_ERR_CUDA;
-  if (cudaStreamSynchronize(s) != cudaSuccess) return FSWIGLU_ERR_CUDA;
-  if (word != 0) {
-    if (cudaMemsetAsync(st->status, 0, sizeof(word), s) != cudaSuccess) return FSWIGLU_ERR_CUDA;
-    if (cudaStreamSynchronize(s) != cudaSuccess) return FSWIGLU_ERR_CUDA;
+  if (int rc = read_and_clear_status(st->status, &word, s)) return rc;
+  // the allocation-free entry point keeps its own word next to its built-in scratch: report it too
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices && g_static[dev].ready) {
+    uint32_t static_word = 0;
+    if (int rc = read_and_clear_status(g_static[dev].dev.status, &static_word, s)) return rc;
+    if (word == 0) word = static_word;
   }
   if (status != nullptr) *status = word;
   return word == 0 ? FSWIGLU_OK : FSWIGLU_ERR_WATCHDOG;
@@ -819,7 +1046,7 @@ const char* fswiglu_status_string(int status) {
   }
 }
 
-const char* fswiglu_version(void) { return "0.1.0"; }
+const char* fswiglu_version(void) { return "0.2.0"; }
 
 uint64_t fswiglu_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 

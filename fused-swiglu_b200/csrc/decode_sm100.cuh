@@ -72,6 +72,10 @@ struct DecodeParams {
   unsigned int* handover; // one counter, zero on entry: CTAs that finished phase 1
   int M;                  // tokens (<= 64)
   int n_pad;              // tokens padded to 16 / 32 / 64 (the MMA N extent)
+  int prefetch_units;     // how many W_down tiles ahead of the shared-memory ring are pulled into L2
+  const float* row_scale; // optional per-token factor on gate and up before SiLU (fused RMSNorm statistic)
+  const void* residual;   // optional bf16 [M, d] added to the output in fp32
+  long long ld_res;
   uint32_t* status;
 };
 
@@ -195,7 +199,18 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
                   fill(&map_up, kb * 64, static_cast<int>(row0), tile_bytes);
         }
       }
+      // Phase 2.  The ring cannot take W_down tiles faster than phase 1 frees its slots, and it
+      // stalls completely while the hand-over is in flight; HBM would idle meanwhile.  So W_down tiles
+      // are pulled into L2 a bounded distance ahead of the ring (fire and forget), and the ring's own
+      // loads then hit L2.  The window is bounded because everything prefetched has to stay in L2
+      // until it is used.
+      long long pf = u_begin + kDecWSlots;
       for (long long u = u_begin; u < u_end && alive; ++u) {
+        for (; pf < u_end && pf < u + kDecWSlots + p.prefetch_units; ++pf) {
+          const int prb = static_cast<int>(pf / p.k_blocks2);
+          const int pkb = static_cast<int>(pf - static_cast<long long>(prb) * p.k_blocks2);
+          tma_prefetch_l2_2d(&map_down, pkb * 64, prb * 128);
+        }
         const int rb = static_cast<int>(u / p.k_blocks2);
         const int kb = static_cast<int>(u - static_cast<long long>(rb) * p.k_blocks2);
         alive = fill(&map_down, kb * 64, rb * 128, 128u * 128u);
@@ -433,16 +448,18 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
 #pragma unroll
           for (int t = 0; t < 16; ++t) {
             if (c0 + t < p.M) {
+              const float rs = p.row_scale != nullptr ? __ldg(p.row_scale + c0 + t) : 1.0f;
               h[static_cast<long long>(c0 + t) * p.F + j] =
-                  __float2bfloat16_rn(silu_mul(__uint_as_float(g[t]), __uint_as_float(uu[t])));
+                  __float2bfloat16_rn(silu_mul(rs * __uint_as_float(g[t]), rs * __uint_as_float(uu[t])));
             }
           }
         }
       }
       release_accumulator();
     }
-    // hand-over: everything this CTA contributes to h is written; count it in
-    __threadfence();
+    // hand-over: everything this CTA contributes to h is written; count it in.  The barrier orders
+    // the 128 threads' stores before thread 0, whose release makes them visible device-wide (one
+    // fence on the critical path instead of one per thread followed by another).
     asm volatile("bar.sync 1, 128;" ::: "memory");
     if (epi_tid == 0 && alive) {
       asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.handover) : "memory");
@@ -486,9 +503,9 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
           }
         }
         release_accumulator();  // accumulator drained: the MMA warp may reuse it
-        __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (epi_tid == 0) {
+          __threadfence();  // the 128 threads' partial sums (ordered before this by the barrier) become visible
           const unsigned int old = atomicAdd(p.counters + rb, 1u);
           *last_flag = (old == static_cast<unsigned int>(nseg - 1)) ? 1u : 0u;
           __threadfence();
@@ -525,10 +542,15 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
             for (int t = 0; t < 16; ++t) {
               if (c0 + t < p.M) {
                 const long long off = static_cast<long long>(c0 + t) * p.ld_out + out_row;
+                float val = a[t];
+                if (p.residual != nullptr) {
+                  val += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.residual)[
+                      static_cast<long long>(c0 + t) * p.ld_res + out_row]);
+                }
                 if (p.out_f32) {
-                  reinterpret_cast<float*>(p.out)[off] = a[t];
+                  reinterpret_cast<float*>(p.out)[off] = val;
                 } else {
-                  reinterpret_cast<__nv_bfloat16*>(p.out)[off] = __float2bfloat16_rn(a[t]);
+                  reinterpret_cast<__nv_bfloat16*>(p.out)[off] = __float2bfloat16_rn(val);
                 }
               }
             }

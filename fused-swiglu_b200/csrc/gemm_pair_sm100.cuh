@@ -1,8 +1,8 @@
 // Two-SM variant of the tiled tcgen05 GEMM: a cluster of two CTAs works on one 256-row tile with
 // `tcgen05.mma.cta_group::2`.  Each CTA loads its own 128 rows of A and only HALF of the B tile
 // (the MMA reads the other half from the partner's shared memory), so a k-block costs each SM
-// 32 KiB of L2 -> SM traffic instead of 48 KiB, and the ring holds 6 stages instead of 4.  No
-// multicast loads are involved: every TMA load is an ordinary per-CTA load.
+// 32 KiB of L2 -> SM traffic instead of 48 KiB, and the ring holds 6 stages instead of 4.  Every
+// TMA load is an ordinary per-CTA load.
 //
 //   rank 0 ("leader")  warp 0 producer, warp 1 MMA issuer for BOTH CTAs, warps 2-5 epilogue
 //   rank 1 ("partner") warp 0 producer (its loads count their bytes on the LEADER's stage barrier),
@@ -13,11 +13,17 @@
 //   kGatedSplit        leader: tile_n rows of W_gate; partner: tile_n rows of W_up
 //   kGatedInterleaved  rows [2 n0 + rank * tile_n, +tile_n) of the packed W1W3
 // so the accumulator columns mean the same as in the one-SM kernel and the epilogue is shared.
-// Results are bit-identical to the one-SM kernel; the host selects this kernel when the problem
-// fills at least one wave of pair tiles.
+//
+// Schedule.  Whole tiles are dealt round-robin to the clusters.  When the tile count is not a
+// multiple of the cluster count the last wave would leave clusters idle; with a scratch buffer
+// from the host the k-blocks of that last wave's tiles are instead cut into equal contiguous ranges,
+// one per cluster (a range covers the end of one tile and the beginning of the next).  A tile shared
+// by several ranges is finished by whichever of them arrives last at the tile's counter: every
+// range publishes its raw fp32 accumulator, the last one sums the blocks in range order (so the
+// result does not depend on timing) and runs the normal epilogue.  Nobody waits for anybody.
 #pragma once
 
-#include "gemm_sm100.cuh"
+#include "gemm_common.cuh"
 
 namespace fsw {
 
@@ -34,6 +40,51 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
       : "memory");
 }
 
+// One unit of a cluster's work list: k-blocks [kb0, kb1) of `tile`.
+struct PairUnit {
+  int tile;
+  int kb0;
+  int kb1;
+  int tail_tile;  // index of the tile among the tail tiles, -1 for a whole-tile unit
+};
+
+// Enumerates the units of one cluster, in the order every role of the CTA pair walks them.
+struct PairSchedule {
+  int cluster_id, num_clusters, num_kb, tail_first, num_tiles;
+  long long g, g_end;  // position and end of this cluster's range in the tail's k-block sequence
+  int tile;            // next whole tile
+
+  __device__ __forceinline__ PairSchedule(const GemmParams& p, int cluster, int clusters, int kb)
+      : cluster_id(cluster), num_clusters(clusters), num_kb(kb), tail_first(p.tail_first),
+        num_tiles(p.num_m_tiles * p.num_n_tiles), tile(cluster) {
+    const long long total = static_cast<long long>(num_tiles - tail_first) * num_kb;
+    g = static_cast<long long>(cluster) * p.tail_len;
+    g_end = min(total, g + p.tail_len);
+  }
+  __device__ __forceinline__ bool next(PairUnit* u) {
+    if (tile < tail_first) {
+      u->tile = tile;
+      u->kb0 = 0;
+      u->kb1 = num_kb;
+      u->tail_tile = -1;
+      tile += num_clusters;
+      return true;
+    }
+    if (g < g_end) {
+      const int tt = static_cast<int>(g / num_kb);
+      const int kb0 = static_cast<int>(g - static_cast<long long>(tt) * num_kb);
+      const int kb1 = static_cast<int>(min(static_cast<long long>(num_kb), kb0 + (g_end - g)));
+      u->tile = tail_first + tt;
+      u->kb0 = kb0;
+      u->kb1 = kb1;
+      u->tail_tile = tt;
+      g += kb1 - kb0;
+      return true;
+    }
+    return false;
+  }
+};
+
 template <int kMode, bool kOutF32>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
@@ -41,15 +92,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_base + kPairStages * kPairStageBytes;
+  // barrier block: full[6], empty[6], tmem_full[2], tmem_empty[2], drain, then bookkeeping words
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (2 * kPairStages + s); };
-  auto tfull_bar = [&](int a) { return bar_base + 8u * (3 * kPairStages + a); };
-  auto tempty_bar = [&](int a) { return bar_base + 8u * (3 * kPairStages + 2 + a); };
-  const uint32_t drain_bar = bar_base + 8u * (3 * kPairStages + 4);
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kPairStages + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kPairStages + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kPairStages + 2 + a); };
+  const uint32_t drain_bar = bar_base + 8u * (2 * kPairStages + 4);
   uint8_t* generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
   volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(
-      generic_base + kPairStages * kPairStageBytes + 8 * (3 * kPairStages + 5));
+      generic_base + kPairStages * kPairStageBytes + 8 * (2 * kPairStages + 5));
   volatile uint32_t* abort_flag = tmem_ptr_slot + 1;
+  volatile uint32_t* epi_ok = tmem_ptr_slot + 2;     // two entries, alternating per unit
+  volatile uint32_t* last_flag = tmem_ptr_slot + 4;  // "this CTA arrived last at the tile's counter"
 
   const int warp = threadIdx.x >> 5;
   const uint32_t lane = lane_id();
@@ -67,6 +121,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
     mbar_init(drain_bar, 1);
     *abort_flag = 0;
+    *last_flag = 0;
     fence_mbar_init();
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b0);
@@ -85,7 +140,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const uint32_t tmem_base = *tmem_ptr_slot;
 
   // p.num_m_tiles counts 256-row pair tiles here
-  const int num_tiles = p.num_m_tiles * p.num_n_tiles;
   const int num_kb = (p.K + kBlockK - 1) / kBlockK;
   const int num_clusters = gridDim.x / 2;
   const int cluster_id = blockIdx.x / 2;
@@ -100,8 +154,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       uint32_t phase = 0;
       uint32_t issued_mask = 0, last_parity_mask = 0;
       bool alive = true;
-      for (int tile = cluster_id; tile < num_tiles && alive; tile += num_clusters) {
-        const TileCoord tc = tile_coord(tile, p);
+      PairSchedule sched(p, cluster_id, num_clusters, num_kb);
+      PairUnit un;
+      while (alive && sched.next(&un)) {
+        const TileCoord tc = tile_coord(un.tile, p);
         const int m0 = tc.m_tile * 256 + static_cast<int>(rank) * 128;
         const int n0 = tc.n_tile * p.tile_n;
         const CUtensorMap* bmap = &map_b0;
@@ -114,7 +170,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         } else {
           b_row = 2 * n0 + static_cast<int>(rank) * b_half_rows;
         }
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = un.kb0; kb < un.kb1; ++kb) {
           if (!wd.wait(empty_bar(stage), phase ^ 1u, kSiteProducerEmpty)) {
             alive = false;
             break;
@@ -164,11 +220,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       int acc = 0;
       uint32_t acc_phase = 0;
       bool alive = true;
-      for (int tile = cluster_id; tile < num_tiles && alive; tile += num_clusters) {
+      PairSchedule sched(p, cluster_id, num_clusters, num_kb);
+      PairUnit un;
+      while (alive && sched.next(&un)) {
         if (!wd.wait<true>(tempty_bar(acc), acc_phase ^ 1u, kSiteMmaTmemEmpty)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kUmmaN);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = un.kb0; kb < un.kb1; ++kb) {
           if (!wd.wait<true>(full_bar(stage), phase, kSiteMmaFull)) {
             alive = false;
             break;
@@ -179,7 +237,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           const uint64_t b_desc = umma_desc_k_sw128(a_addr + kATileBytes);
 #pragma unroll
           for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-            umma_bf16_ss_2cta(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_bf16_ss_2cta(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (kb > un.kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit_pair(empty_bar(stage));  // both CTAs may refill this stage once the MMAs retire
           if (++stage == kPairStages) {
@@ -208,81 +266,83 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int quarter = warp & 3;
     const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t warp_stage = bar_base + 512u + static_cast<uint32_t>(quarter) * (32u * 128u);
+    const int epi_tid = static_cast<int>(threadIdx.x) - 64;
+    const int row_in_half = quarter * 32 + static_cast<int>(lane);
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int tile = cluster_id; tile < num_tiles; tile += num_clusters) {
-      const TileCoord tc = tile_coord(tile, p);
-      uint32_t ok = 1;
-      if (lane == 0) ok = wd.wait(tfull_bar(acc), acc_phase, kSiteEpilogueFull) ? 1u : 0u;
-      ok = __shfl_sync(0xffffffffu, ok, 0);
+    uint32_t iter = 0;
+    PairSchedule sched(p, cluster_id, num_clusters, num_kb);
+    PairUnit un;
+    while (sched.next(&un)) {
+      const TileCoord tc = tile_coord(un.tile, p);
+      // One thread waits for the accumulator and tells the other 127: the four warps share named
+      // barriers below, so they must all take the same exit if a wait gives up.
+      if (epi_tid == 0) epi_ok[iter & 1u] = wd.wait(tfull_bar(acc), acc_phase, kSiteEpilogueFull) ? 1u : 0u;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const uint32_t ok = epi_ok[iter & 1u];
+      ++iter;
       if (!ok) break;
-      __syncwarp();
       tc_fence_after_sync();
       const uint32_t t_acc = tmem_base + lane_field + static_cast<uint32_t>(acc * kUmmaN);
       const int row0 = tc.m_tile * 256 + static_cast<int>(rank) * 128 + quarter * 32;
       const int col_base = tc.n_tile * p.tile_n;
-      const int width = p.tile_n;
-      constexpr int kPiecesPerChunk = kOutF32 ? 1 : 2;
-      int piece = 0, chunk_col0 = col_base, chunk_segs = 0;
-#pragma unroll 1
-      for (int c0 = 0; c0 < width; c0 += 32) {
-        if (col_base + c0 >= p.n_out) break;
-        const int ncols = min(32, width - c0);
-        float v[32];
-        if constexpr (kMode == kPlain) {
-          uint32_t r[32];
-          tmem_ld_cols(t_acc + c0, ncols, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-        } else if constexpr (kMode == kGatedSplit) {
-          uint32_t g[32], u[32];
-          tmem_ld_cols(t_acc + c0, ncols, g);
-          tmem_ld_cols(t_acc + width + c0, ncols, u);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = silu_mul(__uint_as_float(g[i]), __uint_as_float(u[i]));
-        } else {
-          uint32_t lo[32], hi[32];
-          tmem_ld_32x32b_x32(t_acc + 2 * c0, lo);
-          if (ncols == 32) {
-            tmem_ld_32x32b_x32(t_acc + 2 * c0 + 32, hi);
+      auto release_accumulator = [&]() {
+        // this warp is done with the accumulator: tell the leader's MMA issuer (one arrival per warp)
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if (rank == 0) {
+            mbar_arrive(tempty_bar(acc));
           } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) hi[i] = 0u;
-          }
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            v[i] = silu_mul(__uint_as_float(lo[2 * i + 1]), __uint_as_float(lo[2 * i]));
-            v[16 + i] = silu_mul(__uint_as_float(hi[2 * i + 1]), __uint_as_float(hi[2 * i]));
+            mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
           }
         }
-        constexpr int kSegsPerPiece = kOutF32 ? 8 : 4;
-        if (piece == 0) {
-          chunk_col0 = col_base + c0;
-          chunk_segs = 0;
-        }
-        stage_piece<kOutF32>(warp_stage, lane, piece * kSegsPerPiece, ncols, v);
-        chunk_segs += ncols / (kOutF32 ? 4 : 8);
-        if (++piece == kPiecesPerChunk) {
-          drain_chunk<kOutF32>(p, warp_stage, lane, row0, chunk_col0, chunk_segs);
-          piece = 0;
-        }
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      };
+
+      // how many ranges share this tile, and which of them is this cluster's
+      int nseg = 1, seg = 0;
+      if (un.tail_tile >= 0) {
+        const long long t_begin = static_cast<long long>(un.tail_tile) * num_kb;
+        const int first_c = static_cast<int>(t_begin / p.tail_len);
+        const int last_c = static_cast<int>((t_begin + num_kb - 1) / p.tail_len);
+        nseg = last_c - first_c + 1;
+        seg = cluster_id - first_c;
       }
-      if (piece != 0) drain_chunk<kOutF32>(p, warp_stage, lane, row0, chunk_col0, chunk_segs);
-      // this warp is done with the accumulator: tell the leader's MMA issuer (one arrival per warp)
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) {
-        if (rank == 0) {
-          mbar_arrive(tempty_bar(acc));
-        } else {
-          mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
-        }
+      if (nseg == 1) {
+        epilogue_rows<kMode, kOutF32>(p, TmemSource{t_acc}, warp_stage, lane, row0, col_base, p.tile_n);
+        release_accumulator();
+        continue;
       }
-      acc ^= 1;
-      if (acc == 0) acc_phase ^= 1u;
+      // ---- shared tile: publish the raw accumulator, the last range to arrive finishes the tile ----
+      // block of (cluster c, tail tile t) = (c + t) * 2 + rank: consecutive ranges of one tile are
+      // consecutive clusters, so a tile's blocks are 2 * kTailBlockFloats apart
+      float* my_block = p.tail_partials +
+                        (static_cast<long long>(cluster_id + un.tail_tile) * 2 + rank) * kTailBlockFloats;
+      store_partial_row(t_acc, my_block, row_in_half, mma_n);
+      release_accumulator();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (epi_tid == 0) {
+        __threadfence();  // the 128 threads' blocks (ordered before this by the barrier) become visible
+        unsigned int* counter = p.tail_counters + un.tail_tile * 2 + rank;
+        const unsigned int old = atomicAdd(counter, 1u);
+        const bool last = old == static_cast<unsigned int>(nseg - 1);
+        if (last) *counter = 0u;  // every range has arrived: leave the counter clean for the next launch
+        *last_flag = last ? 1u : 0u;
+        __threadfence();
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const bool reduce_here = (*last_flag != 0);
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // everyone has read the flag before it is reused
+      if (reduce_here) {
+        PartialSource src;
+        src.first_block = my_block - static_cast<long long>(seg) * 2 * kTailBlockFloats;
+        src.seg_stride = 2ll * kTailBlockFloats;
+        src.nseg = nseg;
+        src.row = row_in_half;
+        epilogue_rows<kMode, kOutF32>(p, src, warp_stage, lane, row0, col_base, p.tile_n);
+      }
     }
   }
 

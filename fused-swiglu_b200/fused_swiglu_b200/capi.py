@@ -26,10 +26,17 @@ OUT_BF16 = 0
 OUT_F32 = 1
 
 # name -> (restype, argtypes); mirrors include/fswiglu.h one to one.
-_vp, _i64, _int, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t
+_vp, _i64, _int, _sz, _f32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t, ctypes.c_float
 SIGNATURES = {
     "fswiglu_gateup_bf16": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp]),
+    "fswiglu_gateup_bf16_ex": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp, _sz, _vp]),
+    "fswiglu_gemm_scratch_bytes": (_sz, []),
     "fswiglu_down_bf16": (_int, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _int, _vp]),
+    "fswiglu_down_bf16_ex": (_int, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _int, _vp, _i64, _vp, _sz, _vp]),
+    "fswiglu_mlp_bf16_ex": (_int, [_vp, _i64, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _int, _i64, _i64,
+                                   _i64, _vp, _sz, _vp]),
+    "fswiglu_rms_scale_f32": (_int, [_vp, _i64, _i64, _i64, _f32, _vp, _vp]),
+    "fswiglu_static_status": (_int, [ctypes.POINTER(ctypes.c_uint32), _vp]),
     "fswiglu_mlp_bf16": (_int, [_vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _int, _i64, _i64, _i64,
                                 _vp, _sz, _vp]),
     "fswiglu_workspace_bytes": (_sz, [_i64, _i64, _i64]),
@@ -38,7 +45,7 @@ SIGNATURES = {
     "fswiglu_mlp_bf16_static": (_int, [_vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _int, _i64, _i64, _i64, _vp]),
     "fswiglu_cast_f32_to_bf16": (_int, [_vp, _vp, _i64, _vp]),
     "fswiglu_down_scatter_bf16": (_int, [_vp, _i64, _vp, _i64, ctypes.POINTER(ctypes.c_void_p), _int, _int, _i64, _i64,
-                                         _i64, _i64, _vp]),
+                                         _i64, _i64, _vp, _sz, _vp]),
     "fswiglu_reduce_bcast_bf16": (_int, [_vp, ctypes.POINTER(ctypes.c_void_p), _int, _i64, _i64, _int, _vp]),
     "fswiglu_set_max_ctas": (_int, [_int]),
     "fswiglu_device_status": (_int, [ctypes.POINTER(ctypes.c_uint32), _vp]),
@@ -88,6 +95,15 @@ def launch_count() -> int:
 def check(status: int, where: str) -> None:
     if status != OK:
         raise FswigluError(status, where)
+
+
+def static_status(stream_ptr: int = 0) -> int:
+    """Watchdog word of the allocation-free entry point on the current device (0 = healthy)."""
+    word = ctypes.c_uint32(0)
+    rc = lib.fswiglu_static_status(ctypes.byref(word), ctypes.c_void_p(stream_ptr))
+    if rc not in (OK, ERR_WATCHDOG):
+        raise FswigluError(rc, "fswiglu_static_status")
+    return int(word.value)
 
 
 def device_status(stream_ptr: int = 0) -> int:

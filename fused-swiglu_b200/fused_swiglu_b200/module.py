@@ -58,3 +58,44 @@ class FusedSwiGLUMLP(nn.Module):
             x2 = x2.to(torch.bfloat16)
         out = _load_ops().fused_swiglu_mlp_bf16(x2.contiguous(), self.gate_proj, self.up_proj, self.down_proj)
         return out.reshape(*lead, self.hidden_size)
+
+
+class FusedNormSwiGLUBlock(nn.Module):
+    """out = x + down_proj(silu(gate_proj(n)) * up_proj(n)),  n = RMSNorm(x) = x * rsqrt(mean(x^2) + eps) * weight.
+
+    The pre-norm MLP half of a Llama-family block in two kernels instead of six: a one-pass row statistic
+    (`rms_scale`) and the fused MLP, which applies the statistic to its fp32 gate / up accumulators and
+    adds the residual to the fp32 accumulator of the down projection before the single rounding.  The
+    norm's weight vector is multiplied into the columns of gate_proj / up_proj once, by `fold()`; the
+    normalised activations are never written to memory.  Inference only, like the ops.
+    """
+
+    def __init__(self, hidden_size: int, intermediate_size: int, eps: float = 1e-6, device=None):
+        super().__init__()
+        self.mlp = FusedSwiGLUMLP(hidden_size, intermediate_size, device=device)
+        self.norm_weight = nn.Parameter(torch.ones((hidden_size,), dtype=torch.bfloat16, device=device),
+                                        requires_grad=False)
+        self.eps = eps
+        self._folded = None
+
+    def fold(self) -> None:
+        """(Re)compute the gate / up matrices with the norm weight folded in; call after loading weights."""
+        from . import pack
+
+        self._folded = (pack.fold_norm_weight(self.mlp.gate_proj.data, self.norm_weight.data),
+                        pack.fold_norm_weight(self.mlp.up_proj.data, self.norm_weight.data))
+
+    @torch.inference_mode()
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self._folded is None:
+            self.fold()
+        ops = _load_ops()
+        hidden = self.mlp.hidden_size
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, hidden)
+        if x2.dtype != torch.bfloat16:
+            x2 = x2.to(torch.bfloat16)
+        x2 = x2.contiguous()
+        scale = ops.rms_scale(x2, self.eps)
+        out = ops.fused_swiglu_mlp_bf16(x2, self._folded[0], self._folded[1], self.mlp.down_proj, x2, scale, False)
+        return out.reshape(*lead, hidden)

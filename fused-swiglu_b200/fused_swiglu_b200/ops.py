@@ -72,9 +72,47 @@ def fused_swiglu_bf16(X: torch.Tensor, W1W3: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def fused_swiglu_gateup_bf16(x: torch.Tensor, W_gate: torch.Tensor, W_up: torch.Tensor) -> torch.Tensor:
-    """h[M, F] = silu(x W_gate^T) * (x W_up^T) with separate (un-interleaved) weights."""
+def gemm_scratch(device: torch.device | str | int) -> torch.Tensor:
+    """Scratch buffer that lets the two-SM kernel split the reduction of its last, partly filled wave
+    over all SMs (fswiglu_gemm_scratch_bytes).  Share it only between calls ordered on one stream."""
+    return torch.empty(int(capi.lib.fswiglu_gemm_scratch_bytes()), dtype=torch.uint8, device=device)
+
+
+def _check_row_scale(row_scale: torch.Tensor | None, M: int, device) -> None:
+    if row_scale is None:
+        return
+    if row_scale.dtype != torch.float32 or row_scale.device != device or row_scale.numel() != M or \
+            not row_scale.is_contiguous():
+        raise RuntimeError("row_scale must be a contiguous float32 tensor of M elements on the device of x")
+
+
+def _check_residual(residual: torch.Tensor | None, M: int, d: int, device) -> int:
+    if residual is None:
+        return 0
+    if residual.dtype != torch.bfloat16 or residual.device != device or tuple(residual.shape) != (M, d):
+        raise RuntimeError("residual must be a bfloat16 tensor [M, d] on the device of x")
+    return _row_major_ld("residual", residual)
+
+
+def rms_scale(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """scale[r] = rsqrt(mean(x[r]^2) + eps) in fp32: the per-row statistic of RMSNorm, for `row_scale`."""
+    _require_bf16_cuda(x=x)
+    M, d = x.shape
+    scale = torch.empty((M,), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = capi.lib.fswiglu_rms_scale_f32(_vp(x), _row_major_ld("x", x), M, d, float(eps), _vp(scale),
+                                            ctypes.c_void_p(_stream_ptr(x)))
+    capi.check(rc, "rms_scale")
+    return scale
+
+
+def fused_swiglu_gateup_bf16(x: torch.Tensor, W_gate: torch.Tensor, W_up: torch.Tensor,
+                             row_scale: torch.Tensor | None = None,
+                             scratch: torch.Tensor | None = None) -> torch.Tensor:
+    """h[M, F] = silu(s * x W_gate^T) * (s * x W_up^T) with separate (un-interleaved) weights;
+    s = optional per-row factor (see rms_scale)."""
     _require_bf16_cuda(x=x, W_gate=W_gate, W_up=W_up)
+    _check_row_scale(row_scale, x.size(0), x.device)
     M, d = x.shape
     F = W_gate.size(0)
     if W_up.shape != W_gate.shape or W_gate.size(1) != d:
@@ -84,15 +122,18 @@ def fused_swiglu_gateup_bf16(x: torch.Tensor, W_gate: torch.Tensor, W_up: torch.
         raise RuntimeError("W_gate and W_up must share one leading dimension")
     h = torch.empty((M, F), dtype=torch.bfloat16, device=x.device)
     with torch.cuda.device(x.device):
-        rc = capi.lib.fswiglu_gateup_bf16(_vp(x), _row_major_ld("x", x), _vp(W_gate), ldw, _vp(W_up), _vp(h), F,
-                                          M, F, d, 0, ctypes.c_void_p(_stream_ptr(x)))
+        rc = capi.lib.fswiglu_gateup_bf16_ex(_vp(x), _row_major_ld("x", x), _vp(W_gate), ldw, _vp(W_up), _vp(h), F,
+                                             M, F, d, 0, _vp(row_scale), _vp(scratch),
+                                             0 if scratch is None else scratch.numel(),
+                                             ctypes.c_void_p(_stream_ptr(x)))
     capi.check(rc, "fused_swiglu_gateup_bf16")
     return h
 
 
 def swiglu_down_bf16(h: torch.Tensor, W_down: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
-                     out: torch.Tensor | None = None) -> torch.Tensor:
-    """out[M, d] = h W_down^T; bf16 result, or fp32 partial sums for tensor-parallel reduction."""
+                     out: torch.Tensor | None = None, residual: torch.Tensor | None = None,
+                     scratch: torch.Tensor | None = None) -> torch.Tensor:
+    """out[M, d] = (residual +) h W_down^T; bf16 result, or fp32 partial sums for tensor-parallel reduction."""
     _require_bf16_cuda(h=h, W_down=W_down)
     M, F = h.shape
     d = W_down.size(0)
@@ -103,10 +144,13 @@ def swiglu_down_bf16(h: torch.Tensor, W_down: torch.Tensor, out_dtype: torch.dty
     if out is None:
         out = torch.empty((M, d), dtype=out_dtype, device=h.device)
     code = capi.OUT_BF16 if out_dtype == torch.bfloat16 else capi.OUT_F32
+    ldr = _check_residual(residual, M, d, h.device)
     with torch.cuda.device(h.device):
-        rc = capi.lib.fswiglu_down_bf16(_vp(h), _row_major_ld("h", h), _vp(W_down), _row_major_ld("W_down", W_down),
-                                        _vp(out), _row_major_ld("out", out), M, d, F, code,
-                                        ctypes.c_void_p(_stream_ptr(h)))
+        rc = capi.lib.fswiglu_down_bf16_ex(_vp(h), _row_major_ld("h", h), _vp(W_down),
+                                           _row_major_ld("W_down", W_down), _vp(out), _row_major_ld("out", out), M, d,
+                                           F, code, _vp(residual), ldr, _vp(scratch),
+                                           0 if scratch is None else scratch.numel(),
+                                           ctypes.c_void_p(_stream_ptr(h)))
     capi.check(rc, "swiglu_down_bf16")
     return out
 
@@ -119,8 +163,10 @@ def mlp_workspace(M: int, d: int, F: int, device: torch.device | str | int) -> t
 
 def fused_swiglu_mlp_bf16(x: torch.Tensor, W_gate: torch.Tensor, W_up: torch.Tensor, W_down: torch.Tensor,
                           out_dtype: torch.dtype = torch.bfloat16, workspace: torch.Tensor | None = None,
-                          out: torch.Tensor | None = None) -> torch.Tensor:
-    """out[M, d] = (silu(x W_gate^T) * (x W_up^T)) W_down^T in one C-ABI call."""
+                          out: torch.Tensor | None = None, residual: torch.Tensor | None = None,
+                          row_scale: torch.Tensor | None = None) -> torch.Tensor:
+    """out[M, d] = (residual +) (silu(s * x W_gate^T) * (s * x W_up^T)) W_down^T in one C-ABI call;
+    s = optional per-row factor (see rms_scale)."""
     _require_bf16_cuda(x=x, W_gate=W_gate, W_up=W_up, W_down=W_down)
     M, d = x.shape
     F = W_gate.size(0)
@@ -138,11 +184,13 @@ def fused_swiglu_mlp_bf16(x: torch.Tensor, W_gate: torch.Tensor, W_up: torch.Ten
     if workspace is None:
         workspace = mlp_workspace(M, d, F, x.device)
     code = capi.OUT_BF16 if out_dtype == torch.bfloat16 else capi.OUT_F32
+    _check_row_scale(row_scale, M, x.device)
+    ldr = _check_residual(residual, M, d, x.device)
     with torch.cuda.device(x.device):
-        rc = capi.lib.fswiglu_mlp_bf16(_vp(x), _row_major_ld("x", x), _vp(W_gate), _vp(W_up), ldw, _vp(W_down),
-                                       _row_major_ld("W_down", W_down), _vp(out), _row_major_ld("out", out), code,
-                                       M, d, F, _vp(workspace), workspace.numel(),
-                                       ctypes.c_void_p(_stream_ptr(x)))
+        rc = capi.lib.fswiglu_mlp_bf16_ex(_vp(x), _row_major_ld("x", x), _vp(row_scale), _vp(W_gate), _vp(W_up), ldw,
+                                          _vp(W_down), _row_major_ld("W_down", W_down), _vp(residual), ldr,
+                                          _vp(out), _row_major_ld("out", out), code, M, d, F, _vp(workspace),
+                                          workspace.numel(), ctypes.c_void_p(_stream_ptr(x)))
     capi.check(rc, "fused_swiglu_mlp_bf16")
     return out
 

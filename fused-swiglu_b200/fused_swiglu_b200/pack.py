@@ -47,3 +47,12 @@ def shard_mlp_weights(W_gate: torch.Tensor, W_up: torch.Tensor, W_down: torch.Te
     F = W_gate.size(0)
     lo, hi = shard_bounds(F, world_size, rank)
     return (W_gate[lo:hi].contiguous(), W_up[lo:hi].contiguous(), W_down[:, lo:hi].contiguous())
+
+
+def fold_norm_weight(W: torch.Tensor, gamma: torch.Tensor) -> torch.Tensor:
+    """W [F, d] with the RMSNorm weight vector gamma [d] multiplied into its columns (fp32 product,
+    one rounding back to W's dtype): (x * s * gamma) W^T == s * (x (W * gamma)^T), so the norm in front
+    of the MLP costs one statistic per row (ops.rms_scale) and nothing else at run time."""
+    if gamma.dim() != 1 or gamma.numel() != W.size(1):
+        raise ValueError("gamma must have one entry per input feature")
+    return (W.float() * gamma.float().to(W.device)[None, :]).to(W.dtype)

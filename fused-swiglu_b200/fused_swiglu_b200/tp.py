@@ -135,7 +135,8 @@ class TensorParallelSwiGLU:
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.n_slabs_auto = n_slabs <= 0   # push mode: slab heights from plan_slabs()
         self.n_slabs = max(1, n_slabs) if n_slabs > 0 else 4
-        self._gemm_ctas = 148
+        self._gemm_ctas = 148  # replaced by the device's SM count below when there is a device
+        self._prev_max_ctas = None
         self.mode = mode
         self.local_partial = local_partial
         self.round_fn = round_fn
@@ -157,7 +158,25 @@ class TensorParallelSwiGLU:
 
             sms = torch.cuda.get_device_properties(self.device).multi_processor_count
             self._gemm_ctas = max(1, sms - comm_sms)
-            capi.lib.fswiglu_set_max_ctas(self._gemm_ctas)
+            with torch.cuda.device(self.device):
+                self._prev_max_ctas = capi.lib.fswiglu_set_max_ctas(self._gemm_ctas)
+        elif self._cuda:
+            self._gemm_ctas = torch.cuda.get_device_properties(self.device).multi_processor_count
+
+    def close(self) -> None:
+        """Give the SMs that were set aside for the collectives back to this device's GEMM kernels."""
+        if self._prev_max_ctas is not None and self._prev_max_ctas >= 0:
+            from . import capi
+
+            with torch.cuda.device(self.device):
+                capi.lib.fswiglu_set_max_ctas(self._prev_max_ctas)
+        self._prev_max_ctas = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001  (interpreter shutdown: the library may be gone already)
+            pass
 
     @classmethod
     def from_full(cls, w_gate, w_up, w_down, device, group=None, **kw):
@@ -219,6 +238,7 @@ class TensorParallelSwiGLU:
 
                 per = max(r1 - r0 for r0, r1 in self.slab_bounds(M))
                 ws = ops.mlp_workspace(per, self.d, self.F_local, dev)
+                self._scratch = ops.gemm_scratch(dev)
             self._bufs = {key: (partial, out, ws)}
         return self._bufs[key]
 
@@ -344,15 +364,17 @@ class TensorParallelSwiGLU:
                 sp = ctypes.c_void_p(compute.cuda_stream)
                 if self.trace is not None:
                     self.trace("gateup_begin")
-                rc = lib.fswiglu_gateup_bf16(vp(xs), xs.stride(0), vp(self.w_gate), self.w_gate.stride(0), vp(self.w_up),
-                                             vp(h), Fl, rows, Fl, d, 0, sp)
+                rc = lib.fswiglu_gateup_bf16_ex(vp(xs), xs.stride(0), vp(self.w_gate), self.w_gate.stride(0),
+                                                vp(self.w_up), vp(h), Fl, rows, Fl, d, 0, None, vp(self._scratch),
+                                                self._scratch.numel(), sp)
                 capi.check(rc, "fswiglu_gateup_bf16")
                 if self.trace is not None:
                     self.trace("gateup_end")
                 slab_bytes = off * d * 2
                 recv_ptrs = PtrArr(*[b + slab_bytes for b in recv_bases])
                 rc = lib.fswiglu_down_scatter_bf16(vp(h), Fl, vp(self.w_down), self.w_down.stride(0), recv_ptrs, world,
-                                                   rank, rpo, rows, d, Fl, sp)
+                                                   rank, rpo, rows, d, Fl, vp(self._scratch), self._scratch.numel(),
+                                                   sp)
                 capi.check(rc, "fswiglu_down_scatter_bf16")
                 ev = torch.cuda.Event()
                 ev.record(compute)

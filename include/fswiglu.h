@@ -62,6 +62,25 @@ int fswiglu_gateup_bf16(const void* x, int64_t ldx, const void* w_gate_or_w13, i
                         int interleaved, void* stream);
 
 /*
+ * The same stage with its two options (the reference's launcher, csrc/SwiGLU/swiglu.cu:397-525, has
+ * neither):
+ *   row_scale  NULL, or M fp32 factors s_r: the stage computes silu(s_r * (x Wg^T)_r) * (s_r * (x Wu^T)_r),
+ *              i.e. the gate-up projection of the row-normalised input without materialising it.  With
+ *              s_r from fswiglu_rms_scale_f32 and the norm's weight vector folded into the columns of
+ *              W_gate / W_up this is RMSNorm followed by the gate-up stage.
+ *   scratch    NULL, or a 256-byte aligned device buffer of fswiglu_gemm_scratch_bytes() bytes.  With it
+ *              the two-SM kernel splits the reduction of its last, partly filled wave of tiles over all
+ *              SMs (fp32 partial sums combined in a fixed order: deterministic, but the summation order
+ *              of those tiles differs from the unsplit kernel's).  The buffer may be shared by calls
+ *              that are ordered on one stream, not by concurrent ones.
+ */
+int fswiglu_gateup_bf16_ex(const void* x, int64_t ldx, const void* w_gate_or_w13, int64_t ldw,
+                           const void* w_up, void* h, int64_t ldh, int64_t M, int64_t F, int64_t d,
+                           int interleaved, const float* row_scale, void* scratch, size_t scratch_bytes,
+                           void* stream);
+size_t fswiglu_gemm_scratch_bytes(void);
+
+/*
  * Down projection  out = h Wd^T  (absent from the reference, whose kernel stops at h; required by
  * the full-MLP expression (silu(x Wg^T) * (x Wu^T)) Wd^T the build is checked against).
  * out_dtype: FSWIGLU_OUT_BF16 (one rounding of the fp32 accumulator) or FSWIGLU_OUT_F32 (tensor-
@@ -69,6 +88,18 @@ int fswiglu_gateup_bf16(const void* x, int64_t ldx, const void* w_gate_or_w13, i
  */
 int fswiglu_down_bf16(const void* h, int64_t ldh, const void* w_down, int64_t ldw, void* out,
                       int64_t ldo, int64_t M, int64_t d, int64_t F, int out_dtype, void* stream);
+
+/*
+ * The same stage with its two options (no counterpart in the reference):
+ *   residual   NULL, or a bf16 matrix [M, d] with row pitch ldr (16-byte aligned, ldr % 8 == 0,
+ *              d % 8 == 0): out = residual + h Wd^T, added to the fp32 accumulator before the single
+ *              rounding.  May alias `out` element for element (every element is read before it is written
+ *              by the same thread).
+ *   scratch    as for fswiglu_gateup_bf16_ex.
+ */
+int fswiglu_down_bf16_ex(const void* h, int64_t ldh, const void* w_down, int64_t ldw, void* out,
+                         int64_t ldo, int64_t M, int64_t d, int64_t F, int out_dtype, const void* residual,
+                         int64_t ldr, void* scratch, size_t scratch_bytes, void* stream);
 
 /*
  * Whole MLP forward on device buffers:  out = (silu(x Wg^T) * (x Wu^T)) Wd^T.
@@ -84,6 +115,26 @@ int fswiglu_mlp_bf16(const void* x, int64_t ldx, const void* w_gate, const void*
 
 /* Bytes of workspace fswiglu_mlp_bf16 needs for this problem size (0 when M == 0). */
 size_t fswiglu_workspace_bytes(int64_t M, int64_t d, int64_t F);
+
+/*
+ * The transformer block around the MLP, fused (the reference stops at the gate; its benchmark only
+ * gestures at the surrounding module, bench_swiglu.py:22-32):
+ *     out = residual + ( silu(s * (x Wg^T)) * (s * (x Wu^T)) ) Wd^T
+ * row_scale (s, may be NULL) and residual (may be NULL) as described for the two stages above; the
+ * workspace is the one of fswiglu_mlp_bf16.  All batch sizes, including the small-batch path.
+ */
+int fswiglu_mlp_bf16_ex(const void* x, int64_t ldx, const float* row_scale, const void* w_gate,
+                        const void* w_up, int64_t ldw_gu, const void* w_down, int64_t ldw_d,
+                        const void* residual, int64_t ldr, void* out, int64_t ldo, int out_dtype, int64_t M,
+                        int64_t d, int64_t F, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * scale[r] = 1 / sqrt(mean_k x[r, k]^2 + eps) in fp32 for the M rows of the bf16 matrix x [M, d]: the
+ * statistic of RMSNorm, the normalisation in front of the MLP in Llama-family blocks.  One pass over
+ * x (bandwidth bound); feed the result to `row_scale` above.  No counterpart in the reference.
+ */
+int fswiglu_rms_scale_f32(const void* x, int64_t ldx, int64_t M, int64_t d, float eps, float* scale,
+                          void* stream);
 
 /*
  * Same MLP forward with HOST buffers for the activations: x_host [M, d] and out_host [M, d] are
@@ -119,12 +170,26 @@ size_t fswiglu_host_workspace_bytes(int64_t M, int64_t d, int64_t F);
  *     zero when the library is loaded and, by design, stays set after a device-side time-out).  Two
  *     calls whose kernels overlap on the GPU (different streams, no ordering between them) race on
  *     the array and produce garbage: order them.
- *   - The device-side watchdog of this entry point is separate from fswiglu_device_status().
+ *   - When the memory is taken: the array is part of the library's device code image, so the CUDA
+ *     driver reserves its 32 MiB (+256 bytes) on a device when it loads that image there - with the
+ *     default lazy module loading that is the FIRST call into this library on the device, of any entry
+ *     point, not only this one.  A host that hands the GPU to its own pool should make one cheap call
+ *     (for instance fswiglu_static_status) on every device before it sizes the pool.
+ *   - Device-side time-outs of this entry point are recorded in a word next to the array, not in the
+ *     cudaMalloc'd status block the other entry points use.  fswiglu_static_status() reads and clears
+ *     that word without allocating anything; fswiglu_device_status() reports it as well.
  */
 #define FSWIGLU_STATIC_SCRATCH_BYTES (32u << 20)
 int fswiglu_mlp_bf16_static(const void* x, int64_t ldx, const void* w_gate, const void* w_up,
                             int64_t ldw_gu, const void* w_down, int64_t ldw_d, void* out, int64_t ldo,
                             int out_dtype, int64_t M, int64_t d, int64_t F, void* stream);
+/*
+ * Synchronises `stream`, copies the time-out word of fswiglu_mlp_bf16_static on the current device
+ * into *status (0 = healthy), clears it, and returns FSWIGLU_ERR_WATCHDOG if it was set.  Allocates
+ * nothing (also sets the device up like a first fswiglu_mlp_bf16_static call).  No counterpart in the
+ * reference.
+ */
+int fswiglu_static_status(uint32_t* status, void* stream);
 
 /*
  * dst[i] = bf16(src[i]) for n contiguous elements (round to nearest even): the single rounding after
@@ -142,6 +207,7 @@ int fswiglu_cast_f32_to_bf16(const void* src, void* dst, int64_t n, void* stream
  * device pointer; plain stores over NVLink, no TMA on peer memory), at row
  * rank * rows_per_owner + r % rows_per_owner of a [world * rows_per_owner, d] matrix.  The transfer
  * overlaps the GEMM tile by tile.  recv_ptrs is a HOST array of `world` (<= 8) device pointers.
+ * `scratch` is the optional buffer of fswiglu_gateup_bf16_ex (NULL: no split of the last wave).
  *
  * fswiglu_reduce_bcast_bf16: once every rank's stores have landed (the caller separates the two
  * calls by a cross-rank barrier), each rank sums the `world` copies of its own `rows` rows in fp32
@@ -150,7 +216,7 @@ int fswiglu_cast_f32_to_bf16(const void* src, void* dst, int64_t n, void* stream
  */
 int fswiglu_down_scatter_bf16(const void* h, int64_t ldh, const void* w_down, int64_t ldw,
                               void* const* recv_ptrs, int world, int rank, int64_t rows_per_owner, int64_t M,
-                              int64_t d, int64_t F, void* stream);
+                              int64_t d, int64_t F, void* scratch, size_t scratch_bytes, void* stream);
 int fswiglu_reduce_bcast_bf16(const void* recv_local, void* const* out_ptrs, int world, int64_t rows, int64_t cols,
                               int max_ctas, void* stream);
 
@@ -159,8 +225,9 @@ int fswiglu_reduce_bcast_bf16(const void* recv_local, void* const* out_ptrs, int
  * "all SMs".  Tensor-parallel callers reserve a few SMs for the communication kernels that run
  * beside the GEMMs: a persistent GEMM that holds every SM would keep a collective launched later
  * from starting until the GEMM ends, and a collective that got there first would delay some of the
- * GEMM's CTAs to the very end.  Process-wide setting; returns the previous value.  No counterpart in
- * the reference (single GPU).
+ * GEMM's CTAs to the very end.  The setting belongs to the CURRENT device; the call returns the
+ * previous value (or a negative status when the device cannot be used).  No counterpart in the
+ * reference (single GPU).
  */
 int fswiglu_set_max_ctas(int max_ctas);
 
@@ -168,7 +235,7 @@ int fswiglu_set_max_ctas(int max_ctas);
  * Device-side watchdog.  Kernels never spin forever: a wait that exceeds its limit records where it
  * gave up and the kernel unwinds.  This call synchronises `stream`, copies the status word of the
  * current device into *status (0 = healthy), clears it, and returns FSWIGLU_ERR_WATCHDOG if it
- * was non-zero.
+ * was non-zero.  The word of fswiglu_mlp_bf16_static is included once that entry point has been used.
  */
 int fswiglu_device_status(uint32_t* status, void* stream);
 

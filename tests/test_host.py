@@ -30,7 +30,7 @@ def test_library_exports_every_declared_symbol():
 
 def test_status_strings_and_version():
     assert capi.status_string(capi.OK) == "ok"
-    for code in range(-7, 0):
+    for code in range(-8, 0):
         assert capi.status_string(code) != "unknown status"
     assert capi.status_string(-99) == "unknown status"
     assert re.fullmatch(r"\d+\.\d+\.\d+", capi.version())
@@ -165,7 +165,7 @@ def test_torch_extension_surface_loads_without_a_gpu():
     import fused_mlp_module
 
     for name in ("fused_swiglu_bf16", "swiglu_fwd_bf16", "fused_swiglu_gateup_bf16", "swiglu_down_bf16",
-                 "fused_swiglu_mlp_bf16"):
+                 "fused_swiglu_mlp_bf16", "rms_scale"):
         assert callable(getattr(fused_mlp_module, name))
         assert hasattr(torch.ops.ASMLLM, name)
     assert "Tensor X, Tensor W1W3" in str(torch.ops.ASMLLM.fused_swiglu_bf16.default._schema)
@@ -188,7 +188,14 @@ def test_meta_implementations_and_module_shapes():
     assert ops.fused_swiglu_gateup_bf16(x, wg, wg).shape == (12, 40)
     assert ops.fused_swiglu_bf16(x, torch.empty((80, 64), **bf)).shape == (12, 40)
     assert ops.swiglu_down_bf16(torch.empty((12, 40), **bf), wd, True).dtype == torch.float32
-    assert ops.swiglu_fwd_bf16(12, 80, 64, x, 64, torch.empty((80, 64), **bf), 64, torch.empty((12, 80), **bf), 80) is None
+    assert ops.swiglu_fwd_bf16_out(12, 80, 64, x, 64, torch.empty((80, 64), **bf), 64, torch.empty((12, 80), **bf),
+                                   80) is None
+    assert "Tensor(a!) C" in str(ops.swiglu_fwd_bf16_out.default._schema)
+    # the op with the reference's own schema declares no mutation, so it is deliberately not traceable
+    with pytest.raises(NotImplementedError):
+        ops.swiglu_fwd_bf16(12, 80, 64, x, 64, torch.empty((80, 64), **bf), 64, torch.empty((12, 80), **bf), 80)
+    assert ops.rms_scale(x, 1e-6).shape == (12,) and ops.rms_scale(x, 1e-6).dtype == torch.float32
+    assert ops.fused_swiglu_mlp_bf16(x, wg, wg, wd, x, ops.rms_scale(x), True).dtype == torch.float32
     mlp = FusedSwiGLUMLP(64, 40, device="meta")
     assert mlp(torch.empty((2, 3, 64), **bf)).shape == (2, 3, 64)
     assert [n for n, _ in mlp.named_parameters()] == ["gate_proj", "up_proj", "down_proj"]
