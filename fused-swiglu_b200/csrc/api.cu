@@ -359,29 +359,16 @@ int tail_split_k_mode() {  // 0 off, 1 when it pays, 2 always
   return (env[0] == 'f' || env[0] == 'F') ? 2 : 1;
 }
 
-// Decide how the last, partly filled wave of pair tiles is processed (see gemm_pair_sm100.cuh).
-// Splitting pays when the wave would leave enough clusters idle: every shared tile costs a round
-// trip of its 256 KiB accumulator through L2 (a few microseconds), a k-block about a third of one.
+// Decide how the last, partly filled wave of pair tiles is processed (pair_schedule.cuh).
 void plan_pair_tail(GemmParams* p, int clusters, int num_kb, const Scratch& scratch) {
   const int tiles = p->num_m_tiles * p->num_n_tiles;
   p->tail_first = tiles;
   p->tail_len = 0;
   p->tail_partials = nullptr;
   p->tail_counters = nullptr;
-  const int mode = tail_split_k_mode();
-  if (mode == 0 || scratch.ptr == nullptr || scratch.bytes < kTailScratchBytes) return;
-  if (clusters > kTailMaxClusters || clusters < 2) return;
-  const int rem = tiles % clusters;
-  if (rem == 0) return;
-  const long long saved_kb = static_cast<long long>(clusters - rem) * num_kb / clusters;  // per cluster
-  if (mode == 1 && saved_kb < 24) return;
-  long long len = (static_cast<long long>(rem) * num_kb + clusters - 1) / clusters;
-  const long long min_len = (num_kb + kTailMaxSegments - 2) / (kTailMaxSegments - 1);
-  if (len < min_len) len = min_len;
-  if (mode == 1 && len < 4) len = 4;
-  if (len >= num_kb) return;  // nothing to share
-  p->tail_first = tiles - rem;
-  p->tail_len = static_cast<int>(len);
+  if (scratch.ptr == nullptr || scratch.bytes < kTailScratchBytes || clusters > kTailMaxClusters) return;
+  plan_pair_tail_split(tiles, clusters, num_kb, tail_split_k_mode(), &p->tail_first, &p->tail_len);
+  if (p->tail_len == 0) return;
   p->tail_counters = static_cast<unsigned int*>(scratch.ptr);
   p->tail_partials = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch.ptr) + kTailCounterBytes);
 }

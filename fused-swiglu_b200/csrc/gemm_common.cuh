@@ -27,7 +27,6 @@ constexpr int kStoreStageBytes = 4 * 32 * 128;  // per epilogue warp: 32 rows x 
 
 // Split reduction of the last, partly filled wave (two-SM kernel only).  A 128-row half of a pair
 // tile publishes its raw fp32 accumulator (all 256 columns) as one partial block.
-constexpr int kTailMaxSegments = 8;                       // ranges that may share one tile
 constexpr int kTailBlockFloats = 128 * kUmmaN;            // 128 KiB per CTA and segment
 
 struct GemmParams {
@@ -289,7 +288,8 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams& p, const Source&
     const int ncols = min(32, width - c0);  // 32, or 16 for the last piece of an odd width
     float v[32];
     if constexpr (kMode == kPlain) {
-      // residual row segment first, so that its latency overlaps the accumulator read
+      // residual row segment first, so that its latency overlaps the accumulator read (ordinary loads:
+      // the residual may be the output buffer itself; a warp reads a chunk's elements before it writes them)
       uint4 res[4];
       const bool with_res = p.residual != nullptr && row < p.M;
       if (with_res) {
@@ -298,7 +298,7 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams& p, const Source&
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           res[i] = make_uint4(0u, 0u, 0u, 0u);
-          if (8 * i < ncols && col_base + c0 + 8 * i < p.n_out) res[i] = __ldg(reinterpret_cast<const uint4*>(rrow) + i);
+          if (8 * i < ncols && col_base + c0 + 8 * i < p.n_out) res[i] = *(reinterpret_cast<const uint4*>(rrow) + i);
         }
       }
       uint32_t r[32];

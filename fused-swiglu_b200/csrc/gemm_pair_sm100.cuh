@@ -24,6 +24,7 @@
 #pragma once
 
 #include "gemm_common.cuh"
+#include "pair_schedule.cuh"
 
 namespace fsw {
 
@@ -39,51 +40,6 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
       ::"r"(bar), "h"(static_cast<uint16_t>(3))
       : "memory");
 }
-
-// One unit of a cluster's work list: k-blocks [kb0, kb1) of `tile`.
-struct PairUnit {
-  int tile;
-  int kb0;
-  int kb1;
-  int tail_tile;  // index of the tile among the tail tiles, -1 for a whole-tile unit
-};
-
-// Enumerates the units of one cluster, in the order every role of the CTA pair walks them.
-struct PairSchedule {
-  int cluster_id, num_clusters, num_kb, tail_first, num_tiles;
-  long long g, g_end;  // position and end of this cluster's range in the tail's k-block sequence
-  int tile;            // next whole tile
-
-  __device__ __forceinline__ PairSchedule(const GemmParams& p, int cluster, int clusters, int kb)
-      : cluster_id(cluster), num_clusters(clusters), num_kb(kb), tail_first(p.tail_first),
-        num_tiles(p.num_m_tiles * p.num_n_tiles), tile(cluster) {
-    const long long total = static_cast<long long>(num_tiles - tail_first) * num_kb;
-    g = static_cast<long long>(cluster) * p.tail_len;
-    g_end = min(total, g + p.tail_len);
-  }
-  __device__ __forceinline__ bool next(PairUnit* u) {
-    if (tile < tail_first) {
-      u->tile = tile;
-      u->kb0 = 0;
-      u->kb1 = num_kb;
-      u->tail_tile = -1;
-      tile += num_clusters;
-      return true;
-    }
-    if (g < g_end) {
-      const int tt = static_cast<int>(g / num_kb);
-      const int kb0 = static_cast<int>(g - static_cast<long long>(tt) * num_kb);
-      const int kb1 = static_cast<int>(min(static_cast<long long>(num_kb), kb0 + (g_end - g)));
-      u->tile = tail_first + tt;
-      u->kb0 = kb0;
-      u->kb1 = kb1;
-      u->tail_tile = tt;
-      g += kb1 - kb0;
-      return true;
-    }
-    return false;
-  }
-};
 
 template <int kMode, bool kOutF32>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
@@ -154,7 +110,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       uint32_t phase = 0;
       uint32_t issued_mask = 0, last_parity_mask = 0;
       bool alive = true;
-      PairSchedule sched(p, cluster_id, num_clusters, num_kb);
+      PairSchedule sched(p.num_m_tiles * p.num_n_tiles, p.tail_first, p.tail_len, cluster_id, num_clusters, num_kb);
       PairUnit un;
       while (alive && sched.next(&un)) {
         const TileCoord tc = tile_coord(un.tile, p);
@@ -220,7 +176,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       int acc = 0;
       uint32_t acc_phase = 0;
       bool alive = true;
-      PairSchedule sched(p, cluster_id, num_clusters, num_kb);
+      PairSchedule sched(p.num_m_tiles * p.num_n_tiles, p.tail_first, p.tail_len, cluster_id, num_clusters, num_kb);
       PairUnit un;
       while (alive && sched.next(&un)) {
         if (!wd.wait<true>(tempty_bar(acc), acc_phase ^ 1u, kSiteMmaTmemEmpty)) break;
@@ -271,7 +227,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     int acc = 0;
     uint32_t acc_phase = 0;
     uint32_t iter = 0;
-    PairSchedule sched(p, cluster_id, num_clusters, num_kb);
+    PairSchedule sched(p.num_m_tiles * p.num_n_tiles, p.tail_first, p.tail_len, cluster_id, num_clusters, num_kb);
     PairUnit un;
     while (sched.next(&un)) {
       const TileCoord tc = tile_coord(un.tile, p);
@@ -303,13 +259,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
       // how many ranges share this tile, and which of them is this cluster's
       int nseg = 1, seg = 0;
-      if (un.tail_tile >= 0) {
-        const long long t_begin = static_cast<long long>(un.tail_tile) * num_kb;
-        const int first_c = static_cast<int>(t_begin / p.tail_len);
-        const int last_c = static_cast<int>((t_begin + num_kb - 1) / p.tail_len);
-        nseg = last_c - first_c + 1;
-        seg = cluster_id - first_c;
-      }
+      if (un.tail_tile >= 0) tail_tile_segments(un.tail_tile, num_kb, p.tail_len, cluster_id, &nseg, &seg);
       if (nseg == 1) {
         epilogue_rows<kMode, kOutF32>(p, TmemSource{t_acc}, warp_stage, lane, row0, col_base, p.tile_n);
         release_accumulator();
@@ -319,7 +269,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       // block of (cluster c, tail tile t) = (c + t) * 2 + rank: consecutive ranges of one tile are
       // consecutive clusters, so a tile's blocks are 2 * kTailBlockFloats apart
       float* my_block = p.tail_partials +
-                        (static_cast<long long>(cluster_id + un.tail_tile) * 2 + rank) * kTailBlockFloats;
+                        (static_cast<long long>(tail_block_index(cluster_id, un.tail_tile)) * 2 + rank) * kTailBlockFloats;
       store_partial_row(t_acc, my_block, row_in_half, mma_n);
       release_accumulator();
       asm volatile("bar.sync 1, 128;" ::: "memory");

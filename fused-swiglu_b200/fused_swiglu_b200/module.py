@@ -48,7 +48,7 @@ class FusedSwiGLUMLP(nn.Module):
             mod.down_proj.copy_(down_proj.weight)
         return mod
 
-    @torch.inference_mode()
+    @torch.no_grad()
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if x.size(-1) != self.hidden_size:
             raise RuntimeError(f"expected last dimension {self.hidden_size}, got {x.size(-1)}")
@@ -85,7 +85,7 @@ class FusedNormSwiGLUBlock(nn.Module):
         self._folded = (pack.fold_norm_weight(self.mlp.gate_proj.data, self.norm_weight.data),
                         pack.fold_norm_weight(self.mlp.up_proj.data, self.norm_weight.data))
 
-    @torch.inference_mode()
+    @torch.no_grad()
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self._folded is None:
             self.fold()

@@ -150,7 +150,10 @@ class TensorParallelSwiGLU:
         # explicit slab heights (rows), e.g. [3840, 3840, 512]; every slab but the last must be a
         # multiple of 8 * world.  None: n_slabs equal slabs.
         self.slab_rows = list(slab_rows) if slab_rows else None
-        self.trace = None  # optional callable(tag): "gateup_begin" / "gateup_end" around that launch (push mode)
+        # optional callable(tag, slab, stream), push mode: called at "gateup_begin", "gateup_end", "down_end" (compute
+        # stream), "barrier_end", "reduce_end" (communication stream) of every slab and at "final_barrier_end" (slab
+        # -1); a benchmark records an event on `stream` there to time the phases
+        self.trace = None
         if self._cuda and self.world > 1 and comm_sms > 0:
             # leave `comm_sms` SMs to the collective kernels that run beside the GEMMs (the launcher
             # should cap NCCL to the same number, e.g. NCCL_MAX_CTAS), see fswiglu_set_max_ctas
@@ -363,31 +366,39 @@ class TensorParallelSwiGLU:
                 h = ws[: rows * Fl * 2].view(torch.bfloat16).view(rows, Fl)
                 sp = ctypes.c_void_p(compute.cuda_stream)
                 if self.trace is not None:
-                    self.trace("gateup_begin")
+                    self.trace("gateup_begin", si, compute)
                 rc = lib.fswiglu_gateup_bf16_ex(vp(xs), xs.stride(0), vp(self.w_gate), self.w_gate.stride(0),
                                                 vp(self.w_up), vp(h), Fl, rows, Fl, d, 0, None, vp(self._scratch),
                                                 self._scratch.numel(), sp)
                 capi.check(rc, "fswiglu_gateup_bf16")
                 if self.trace is not None:
-                    self.trace("gateup_end")
+                    self.trace("gateup_end", si, compute)
                 slab_bytes = off * d * 2
                 recv_ptrs = PtrArr(*[b + slab_bytes for b in recv_bases])
                 rc = lib.fswiglu_down_scatter_bf16(vp(h), Fl, vp(self.w_down), self.w_down.stride(0), recv_ptrs, world,
                                                    rank, rpo, rows, d, Fl, vp(self._scratch), self._scratch.numel(),
                                                    sp)
                 capi.check(rc, "fswiglu_down_scatter_bf16")
+                if self.trace is not None:
+                    self.trace("down_end", si, compute)
                 ev = torch.cuda.Event()
                 ev.record(compute)
                 comm.wait_event(ev)
                 with torch.cuda.stream(comm):
                     self._recv_hdl.barrier(channel=si % 4)  # every rank's partial rows of this slab have landed
+                    if self.trace is not None:
+                        self.trace("barrier_end", si, comm)
                     out_ptrs = PtrArr(*[b + (off + rank * rpo) * d * 2 for b in out_bases])
                     rc = lib.fswiglu_reduce_bcast_bf16(ctypes.c_void_p(recv_bases[rank] + slab_bytes), out_ptrs, world,
                                                        rpo, d, self._reduce_ctas, ctypes.c_void_p(comm.cuda_stream))
                     capi.check(rc, "fswiglu_reduce_bcast_bf16")
+                    if self.trace is not None:
+                        self.trace("reduce_end", si, comm)
                 off += rows_p
             with torch.cuda.stream(comm):
                 self._out_hdl.barrier(channel=0)  # every rank's result rows have landed everywhere
+                if self.trace is not None:
+                    self.trace("final_barrier_end", -1, comm)
             compute.wait_stream(comm)
         if out.size(0) != M:
             pieces, off = [], 0

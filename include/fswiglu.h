@@ -93,8 +93,8 @@ int fswiglu_down_bf16(const void* h, int64_t ldh, const void* w_down, int64_t ld
  * The same stage with its two options (no counterpart in the reference):
  *   residual   NULL, or a bf16 matrix [M, d] with row pitch ldr (16-byte aligned, ldr % 8 == 0,
  *              d % 8 == 0): out = residual + h Wd^T, added to the fp32 accumulator before the single
- *              rounding.  May alias `out` element for element (every element is read before it is written
- *              by the same thread).
+ *              rounding.  May be `out` itself (same base and pitch): the warp that writes a group of
+ *              elements has read them first.
  *   scratch    as for fswiglu_gateup_bf16_ex.
  */
 int fswiglu_down_bf16_ex(const void* h, int64_t ldh, const void* w_down, int64_t ldw, void* out,

@@ -109,6 +109,24 @@ def mlp_bf16_pipeline(x, w_gate, w_up, w_down, round_out: bool = True) -> np.nda
     return bf16_round(out) if round_out else out
 
 
+def rms_scale(x: np.ndarray, eps: float = 1e-6) -> np.ndarray:
+    """Per-row RMSNorm statistic rsqrt(mean(x^2) + eps) in fp32 (float64 accumulation of the mean)."""
+    x = np.asarray(x, np.float32)
+    ms = (x.astype(np.float64) ** 2).mean(axis=1)
+    return (1.0 / np.sqrt(ms + eps)).astype(np.float32)
+
+
+def norm_mlp_residual_fp32(x, gamma, w_gate, w_up, w_down, eps: float = 1e-6, residual=None) -> np.ndarray:
+    """The pre-norm MLP half of a transformer block in fp32:
+    out = residual + (silu(n Wg^T) * (n Wu^T)) Wd^T with n = x * rsqrt(mean(x^2) + eps) * gamma.
+    The reference has no counterpart (its kernel stops at the gate); this is the expression the fused
+    row-scale / residual options of the GPU path are held to."""
+    x = np.asarray(x, np.float32)
+    n = x * rms_scale(x, eps)[:, None] * np.asarray(gamma, np.float32)[None, :]
+    out = mlp_fp32(n, w_gate, w_up, w_down)
+    return out if residual is None else out + np.asarray(residual, np.float32)
+
+
 def mlp_tp_partials(x, w_gate, w_up, w_down, world_size: int, bounds) -> list[np.ndarray]:
     """fp32 partial outputs of a Megatron split over F: rank r uses rows [lo,hi) of W_gate / W_up and
     columns [lo,hi) of W_down, `bounds(F, world_size, r) -> (lo, hi)`.  Their sum is the MLP output."""

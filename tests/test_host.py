@@ -156,7 +156,7 @@ def test_bench_reference_arm_prints_one_json_line():
     j = json.loads(lines[0])
     assert j["impl"] == "reference" and j["unit"] == "TFLOP/s" and j["value"] > 0
     assert j["cpu_baseline"]["kind"] == "port" and j["e2e"]["h2d_bytes_per_step"] == 0
-    assert j["config"]["workload"] == "c2_llama2_7b_prefill"
+    assert j["config"]["workload"] == "c4_llama3_70b_prefill"
 
 
 def test_torch_extension_surface_loads_without_a_gpu():
@@ -204,3 +204,42 @@ def test_meta_implementations_and_module_shapes():
     lin = torch.nn.Linear(64, 40, bias=False)
     m2 = FusedSwiGLUMLP.from_linears(lin, torch.nn.Linear(64, 40, bias=False), torch.nn.Linear(40, 64, bias=False))
     assert m2.gate_proj.dtype == torch.bfloat16 and torch.equal(m2.gate_proj.float(), lin.weight.to(torch.bfloat16).float())
+
+
+def test_pair_kernel_schedule_arithmetic(tmp_path):
+    """The work list of the two-SM GEMM kernel and the plan of its split last wave are plain integer
+    code shared by host and device (csrc/pair_schedule.cuh): compile the checker with g++ and run it."""
+    import subprocess
+
+    exe = tmp_path / "check_pair_schedule"
+    src = os.path.join(ROOT, "tests", "native", "check_pair_schedule.cpp")
+    inc = os.path.join(ROOT, "fused-swiglu_b200", "csrc")
+    subprocess.run(["g++", "-O1", "-std=c++17", f"-I{inc}", src, "-o", str(exe)], check=True)
+    res = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0 and res.stdout.startswith("ok "), res.stdout[-400:]
+
+
+def test_graph_capture_traces_through_the_ops():
+    """torch.compile(fullgraph=True) must trace the module and the alias-annotated launcher without a graph
+    break; on a CPU-only machine the captured graph then fails at run time, with the dispatcher's missing
+    CPU kernel error and nothing else (the GPU suite runs the same graphs for real)."""
+    import fused_mlp_module  # noqa: F401
+    from fused_swiglu_b200.module import FusedNormSwiGLUBlock, FusedSwiGLUMLP
+
+    if torch.cuda.is_available():
+        pytest.skip("covered with real tensors by the GPU suite")
+    bf = dict(dtype=torch.bfloat16)
+    x = torch.zeros((2, 3, 64), **bf)
+    for mod in (FusedSwiGLUMLP(64, 40), FusedNormSwiGLUBlock(64, 40)):
+        torch._dynamo.reset()
+        with pytest.raises(NotImplementedError, match="'CPU' backend"):
+            torch.compile(mod, fullgraph=True, backend="aot_eager")(x)
+
+    def launch(A, B, C):
+        torch.ops.ASMLLM.swiglu_fwd_bf16_out(12, 80, 64, A, 64, B, 64, C, 80)
+        return C * 2
+
+    torch._dynamo.reset()
+    with pytest.raises(NotImplementedError, match="'CPU' backend"):
+        torch.compile(launch, fullgraph=True, backend="aot_eager")(torch.zeros((12, 64), **bf), torch.zeros((80, 64), **bf),
+                                                                    torch.zeros((12, 80), **bf))

@@ -5,7 +5,9 @@ afford the device-wide synchronisation of cudaMalloc).  Its hidden activations l
 
 Checked here, through the C ABI: the result is bit-identical to fswiglu_mlp_bf16 on two calls in a
 row with different inputs and sizes (the array keeps the first call's contents, which must not leak
-into the second), and a problem larger than the array is refused with FSWIGLU_ERR_TOO_LARGE.
+into the second), a warm call leaves the driver's free-memory figure and torch's allocator counters
+unchanged, its time-out word can be read, and a problem larger than the array is refused with
+FSWIGLU_ERR_TOO_LARGE.
 The file name sorts last on purpose: a run that stops at the first failure has then already run
 every other test.
 """
@@ -44,7 +46,34 @@ def test_static_scratch_entry_point_matches_workspace_entry_point(cuda_dev):
         torch.cuda.synchronize()
         # same kernels, same tile schedule, same rounding points: the tolerance is zero
         assert torch.equal(got, want), f"case M={M} d={d} F={F}"
+    # the time-out word of this entry point sits next to its array; both status calls report it
+    assert capi.static_status() == 0
     assert capi.device_status() == 0
+
+
+def test_static_scratch_entry_point_allocates_nothing(cuda_dev):
+    """What the entry point is for: a warm call must not take device memory from anybody.  Checked on
+    both levels: the driver's free-memory figure (cudaMemGetInfo) and torch's caching-allocator counters
+    are the same before and after a call, and so is the launch path's own bookkeeping."""
+    import fused_swiglu_b200 as fsw
+
+    lib, capi = fsw.capi.lib, fsw.capi
+    x, wg, wu, wd = (t.to(cuda_dev) for t in fsw.inputs.make_mlp_inputs(300, 520, 1096, seed=0))
+    out = torch.empty((300, 520), dtype=torch.bfloat16, device=cuda_dev)
+    assert _static_mlp(lib, x, wg, wu, wd, capi.OUT_BF16, out) == capi.OK  # first call on the device: set-up
+    assert capi.static_status() == 0
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info(cuda_dev)
+    stats_before = torch.cuda.memory_stats(cuda_dev)
+    for _ in range(3):
+        assert _static_mlp(lib, x, wg, wu, wd, capi.OUT_BF16, out) == capi.OK
+    torch.cuda.synchronize()
+    assert capi.static_status() == 0
+    free_after, _ = torch.cuda.mem_get_info(cuda_dev)
+    stats_after = torch.cuda.memory_stats(cuda_dev)
+    assert free_after == free_before, "device memory was taken during a warm call"
+    for key in ("allocation.all.allocated", "segment.all.allocated", "reserved_bytes.all.current"):
+        assert stats_after[key] == stats_before[key], key
 
 
 def test_static_scratch_entry_point_refuses_oversized_problems(cuda_dev):
