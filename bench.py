@@ -278,10 +278,16 @@ def kernel_name(M, n_out, tile, sms, gated):
             else f"gemm_tcgen05_kernel<{mode}> (one-SM tcgen05)")
 
 
-def tensor_roofline(name, rows, d, Fl, gateup_ms, n_launches, region_ms, sms, world):
+def tensor_roofline(name, rows, d, Fl, gateup_ms, n_launches, region_ms, sms, world, clocks=None):
+    """Denominator: the measured cuBLAS bf16 peak of the regime the timed region ran in - the burst figure
+    while the GPU still boosts, the sustained one once the 1 kW power cap sets the clock (a region of
+    half a second or more, or a median SM clock under 85 % of the maximum while it ran)."""
     peaks, peak_src = measured_peaks()
-    long_region = region_ms >= 500.0
-    peak = peaks["bf16_tflops_sustained"] if long_region else peaks["bf16_tflops"]
+    capped = False
+    if clocks and clocks.get("sm_mhz") and clocks.get("sm_max_mhz"):
+        capped = clocks["sm_mhz"] < 0.85 * clocks["sm_max_mhz"]
+    sustained = region_ms >= 500.0 or capped
+    peak = peaks["bf16_tflops_sustained"] if sustained else peaks["bf16_tflops"]
     flops = 4.0 * rows * d * Fl
     achieved = flops / (gateup_ms * 1e-3) / 1e12
     frac = achieved / peak
@@ -289,7 +295,9 @@ def tensor_roofline(name, rows, d, Fl, gateup_ms, n_launches, region_ms, sms, wo
     traffic = NCU_TRAFFIC_BYTES.get(name) if world == 1 else None
     return {"bound": "tensor", "kernel": kernel_name(rows, Fl, 128, sms, True) + ": gate-up + SiLU*up",
             "achieved": achieved, "peak": peak, "unit": UNIT, "frac": frac, "traffic": traffic,
-            "peak_source": f"{peak_src} {'sustained' if long_region else 'burst'} cuBLAS bf16",
+            "peak_source": f"{peak_src} {'sustained' if sustained else 'burst'} cuBLAS bf16",
+            "frac_of_burst_peak": achieved / peaks["bf16_tflops"],
+            "frac_of_sustained_peak": achieved / peaks["bf16_tflops_sustained"],
             "frac_of_nominal_2250": achieved / NOMINAL_BF16_TFLOPS, "flops_per_launch": flops,
             "rows_per_launch": rows, "ms_per_launch": gateup_ms, "launches_timed": n_launches}
 
@@ -388,7 +396,7 @@ def run_single_prefill(name, args, dev, stream, local_rank, with_parity, with_su
     M, d, F = w.M, w.d, w.F
     rec = {"workload": name, "value": flops_mlp(M, d, F) / (ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms,
            "steps": args.steps, "tokens_per_s": M / (ms * 1e-3),
-           "roofline": tensor_roofline(name, M, d, F, gu_ms, len(w.events), total_ms, sms, 1),
+           "roofline": tensor_roofline(name, M, d, F, gu_ms, len(w.events), total_ms, sms, 1, sampler.summary()),
            "kernels": {"gate_up": {"kernel": kernel_name(M, F, 128, sms, True), "ms": gu_ms,
                                    "tflops": 4.0 * M * d * F / (gu_ms * 1e-3) / 1e12},
                        "down": {"kernel": kernel_name(M, d, 256, sms, False), "ms": dn_ms,
@@ -730,7 +738,7 @@ def run_tensor_parallel(args, rank, local_rank, world):
         rows = bounds[tall][1] - bounds[tall][0]
         gu_ms = gateup_by_slab.get(tall)
         roofline = (tensor_roofline(name, rows, d, Fl, gu_ms, len(marks.get((tall, "gateup_begin"), [])), total_ms, sms,
-                                    world) if gu_ms else None)
+                                    world, sampler.summary()) if gu_ms else None)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,

@@ -144,6 +144,8 @@ struct DeviceState {
 std::mutex g_mutex;
 DeviceState g_dev[kMaxDevices];
 std::atomic<uint64_t> g_launches{0};
+std::atomic<unsigned long long> g_wait_limit_ns{kWaitLimitNs};
+std::atomic<int> g_withhold_one_copy{0};  // test aid, consumed by the next launch (see fswiglu_test_expire_next_wait)
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                    const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -310,7 +312,10 @@ int launch_gemm(const DeviceState& st, const CUtensorMap& ma, const CUtensorMap&
   const int units = p.split_from + 2 * (tiles - p.split_from);
   const int ctas = effective_ctas(st);
   const int grid = units < ctas ? units : ctas;
-  gemm_tcgen05_kernel<kMode, kOutF32><<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(ma, mb0, mb1, p);
+  GemmParams q = p;
+  q.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
+  q.withhold_one_copy = g_withhold_one_copy.exchange(0, std::memory_order_relaxed);
+  gemm_tcgen05_kernel<kMode, kOutF32><<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(ma, mb0, mb1, q);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError() == cudaSuccess ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
 }
@@ -396,6 +401,8 @@ int launch_gemm_pair(const DeviceState& st, const void* a, int64_t lda, const vo
   if (p.tail_len > 0 && !scratch.counters_clean) {
     if (cudaMemsetAsync(p.tail_counters, 0, kTailCounterBytes, stream) != cudaSuccess) return FSWIGLU_ERR_CUDA;
   }
+  p.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
+  p.withhold_one_copy = g_withhold_one_copy.exchange(0, std::memory_order_relaxed);
   gemm_pair_kernel<kMode, kOutF32><<<2 * clusters, kGemmThreads, kPairSmemBytes, stream>>>(ma, mb0, mb1, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError() == cudaSuccess ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
@@ -556,6 +563,7 @@ int decode_impl(DeviceState& st, const void* x, int64_t ldx, const void* w_gate,
   p.residual = fu.residual;
   p.ld_res = fu.ld_res;
   p.status = st.status;
+  p.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
 
   CUtensorMap m_gate, m_up, m_x, m_down, m_h;
   if ((rc = encode_map(&m_gate, w_gate, F, d, ldw_gu, p.tile_rows))) return rc;
@@ -570,6 +578,8 @@ int decode_impl(DeviceState& st, const void* x, int64_t ldx, const void* w_gate,
     if ((rc = encode_map(&m_gate, w_gate, F, d, ldw_gu, p.tile_rows))) return rc;
     if ((rc = encode_map(&m_up, w_up, F, d, ldw_gu, p.tile_rows))) return rc;
   }
+  p.handover_target = static_cast<unsigned int>(grid) +
+                      static_cast<unsigned int>(g_withhold_one_copy.exchange(0, std::memory_order_relaxed) != 0 ? 1 : 0);
   // Cooperative launch: the phase hand-over needs every CTA resident at the same time.
   void* args[] = {&m_gate, &m_up, &m_down, &m_x, &m_h, &p};
   const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(decode_fused_kernel), dim3(grid),
@@ -999,6 +1009,13 @@ int fswiglu_set_max_ctas(int max_ctas) {
   st->max_ctas = max_ctas < 0 ? 0 : max_ctas;
   return prev;
 }
+
+int64_t fswiglu_set_wait_limit_us(int64_t limit_us) {
+  const unsigned long long ns = limit_us > 0 ? static_cast<unsigned long long>(limit_us) * 1000ull : kWaitLimitNs;
+  return static_cast<int64_t>(g_wait_limit_ns.exchange(ns, std::memory_order_relaxed) / 1000ull);
+}
+
+void fswiglu_test_expire_next_wait(int enable) { g_withhold_one_copy.store(enable != 0 ? 1 : 0, std::memory_order_relaxed); }
 
 int fswiglu_device_status(uint32_t* status, void* stream) {
   DeviceState* st = nullptr;

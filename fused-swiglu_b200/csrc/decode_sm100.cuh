@@ -77,6 +77,9 @@ struct DecodeParams {
   const void* residual;   // optional bf16 [M, d] added to the output in fp32
   long long ld_res;
   uint32_t* status;
+  unsigned long long wait_limit_ns;  // limit of every device-side wait in this launch
+  unsigned int handover_target;      // CTAs that must have finished phase 1 (= the grid size; tests of the
+                                     // time-out path pass one more, which nothing ever reaches)
 };
 
 // First unit of CTA c when `units` units are cut into `ctas` contiguous ranges.
@@ -123,7 +126,7 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
 
   const int warp = threadIdx.x >> 5;
   const uint32_t lane = lane_id();
-  const Watchdog wd{abort_flag, p.status};
+  const Watchdog wd{abort_flag, p.status, p.wait_limit_ns};
 
   constexpr int kAccStride = 128;  // TMEM columns per accumulator stage (2 stages)
   const uint32_t x_slot_bytes = static_cast<uint32_t>(p.n_pad) * 128u;
@@ -221,7 +224,7 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
             const uint32_t par = (last_parity_mask >> s) & 1u;
             const unsigned long long t0 = global_timer_ns();
             while (!mbar_try_wait(w_full(s), par)) {
-              if (global_timer_ns() - t0 > 50000000ull) {
+              if (global_timer_ns() - t0 > kDrainLimitNs) {
                 wd.give_up(kSiteDrainTma);
                 break;
               }
@@ -257,13 +260,13 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
       if (alive && u_begin < u_end) {
         // h is complete once every CTA has counted itself in (release/acquire through the counter)
         const unsigned long long t0 = global_timer_ns();
-        while (ld_acquire_gpu(p.handover) < gridDim.x) {
+        while (ld_acquire_gpu(p.handover) < p.handover_target) {
           __nanosleep(32);
           if (wd.aborted()) {
             alive = false;
             break;
           }
-          if (global_timer_ns() - t0 > kWaitLimitNs) {
+          if (global_timer_ns() - t0 > p.wait_limit_ns) {
             wd.give_up(kSiteDecode);
             alive = false;
             break;
@@ -281,7 +284,7 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
             const uint32_t par = (last_parity_mask >> s) & 1u;
             const unsigned long long t0 = global_timer_ns();
             while (!mbar_try_wait(x_full(s), par)) {
-              if (global_timer_ns() - t0 > 50000000ull) {
+              if (global_timer_ns() - t0 > kDrainLimitNs) {
                 wd.give_up(kSiteDrainTma);
                 break;
               }
@@ -392,7 +395,7 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
         umma_commit(drain_bar);
         const unsigned long long t0 = global_timer_ns();
         while (!mbar_try_wait(drain_bar, 0)) {
-          if (global_timer_ns() - t0 > 50000000ull) {
+          if (global_timer_ns() - t0 > kDrainLimitNs) {
             wd.give_up(kSiteDrainMma);
             break;
           }

@@ -57,6 +57,11 @@ struct GemmParams {
   float* tail_partials;          // [(cluster + tail tile) * 2 + cta rank][kTailBlockFloats]
   unsigned int* tail_counters;   // [tail tile * 2 + cta rank], zero on entry, zero again on exit
   uint32_t* status;   // device watchdog word (0 = healthy)
+  unsigned long long wait_limit_ns;  // limit of every device-side wait in this launch
+  // Test aid for the time-out path: when non-zero, the first CTA (the leader of the first pair) leaves
+  // out one operand copy of its first k-block, so the wait for that k-block's bytes runs out, the CTA
+  // unwinds and the launch reports a time-out instead of a result.  Never set outside tests.
+  int withhold_one_copy;
   // Optional fusions.
   const float* row_scale;        // gated modes: per-row factor applied to gate and up before SiLU
   const void* residual;          // plain mode: bf16 [M, n_out] added to the accumulator in fp32

@@ -64,7 +64,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int warp = threadIdx.x >> 5;
   const uint32_t lane = lane_id();
   const uint32_t rank = cluster_ctarank();  // 0 = leader
-  const Watchdog wd{abort_flag, p.status};
+  const Watchdog wd{abort_flag, p.status, p.wait_limit_ns};
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kPairStages; ++s) {
@@ -112,6 +112,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       bool alive = true;
       PairSchedule sched(p.num_m_tiles * p.num_n_tiles, p.tail_first, p.tail_len, cluster_id, num_clusters, num_kb);
       PairUnit un;
+      bool withhold = p.withhold_one_copy != 0 && blockIdx.x == 0;  // one-shot, leader of the first pair
       while (alive && sched.next(&un)) {
         const TileCoord tc = tile_coord(un.tile, p);
         const int m0 = tc.m_tile * 256 + static_cast<int>(rank) * 128;
@@ -136,7 +137,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2u * stage_tx_bytes);
           const uint32_t leader_full = map_to_cta(full_bar(stage), 0);
           tma_load_2d_pair(a_dst, &map_a, leader_full, kb * kBlockK, m0);
-          tma_load_2d_pair(a_dst + kATileBytes, bmap, leader_full, kb * kBlockK, b_row);
+          if (!withhold) tma_load_2d_pair(a_dst + kATileBytes, bmap, leader_full, kb * kBlockK, b_row);
+          withhold = false;
           issued_mask |= 1u << stage;
           last_parity_mask = (last_parity_mask & ~(1u << stage)) | (phase << stage);
           if (++stage == kPairStages) {
@@ -152,7 +154,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               const uint32_t par = (last_parity_mask >> s) & 1u;
               const unsigned long long t0 = global_timer_ns();
               while (!mbar_try_wait(full_bar(s), par)) {
-                if (global_timer_ns() - t0 > 50000000ull) {
+                if (global_timer_ns() - t0 > kDrainLimitNs) {
                   wd.give_up(kSiteDrainTma);
                   break;
                 }
@@ -210,7 +212,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         umma_commit_2cta(drain_bar);
         const unsigned long long t0 = global_timer_ns();
         while (!mbar_try_wait(drain_bar, 0)) {
-          if (global_timer_ns() - t0 > 50000000ull) {
+          if (global_timer_ns() - t0 > kDrainLimitNs) {
             wd.give_up(kSiteDrainMma);
             break;
           }

@@ -87,7 +87,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 
   const int warp = threadIdx.x >> 5;
   const uint32_t lane = lane_id();
-  const Watchdog wd{abort_flag, p.status};
+  const Watchdog wd{abort_flag, p.status, p.wait_limit_ns};
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -146,7 +146,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
           const uint32_t b_dst = a_dst + kATileBytes;
           mbar_arrive_expect_tx(full_bar(stage), stage_tx_bytes);
           tma_load_2d(a_dst, &map_a, full_bar(stage), kb * kBlockK, m0);
-          tma_load_2d(b_dst, &map_b0, full_bar(stage), kb * kBlockK, b_row);
+          if (!(p.withhold_one_copy != 0 && blockIdx.x == 0 && unit == 0 && kb == 0)) {
+            tma_load_2d(b_dst, &map_b0, full_bar(stage), kb * kBlockK, b_row);
+          }
           if (two_boxes) {
             tma_load_2d(b_dst + half_rows * (kBlockK * 2), &map_b0, full_bar(stage), kb * kBlockK, b_row + half_rows);
           }
@@ -173,7 +175,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             const uint32_t par = (last_parity_mask >> s) & 1u;
             const unsigned long long t0 = global_timer_ns();
             while (!mbar_try_wait(full_bar(s), par)) {
-              if (global_timer_ns() - t0 > 50000000ull) {  // 50 ms
+              if (global_timer_ns() - t0 > kDrainLimitNs) {  // 50 ms
                 wd.give_up(kSiteDrainTma);
                 break;
               }
@@ -228,7 +230,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         umma_commit(drain_bar);
         const unsigned long long t0 = global_timer_ns();
         while (!mbar_try_wait(drain_bar, 0)) {
-          if (global_timer_ns() - t0 > 50000000ull) {
+          if (global_timer_ns() - t0 > kDrainLimitNs) {
             wd.give_up(kSiteDrainMma);
             break;
           }

@@ -25,7 +25,8 @@ enum WaitSite : uint32_t {
   kSitePeer = 8,            // 2-CTA pair handshakes
 };
 
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s: default limit of every device-side wait
+constexpr unsigned long long kDrainLimitNs = 50000000ull;   // 50 ms: copies / MMAs in flight during an unwind
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -52,18 +53,8 @@ __device__ __forceinline__ void fence_mbar_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
 
-// Make generic-proxy writes to shared memory visible to the async proxy (TMA / MMA).
-__device__ __forceinline__ void fence_proxy_async_smem() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
 }
 
@@ -111,6 +102,7 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
 struct Watchdog {
   volatile uint32_t* abort_flag;  // shared memory
   uint32_t* status;               // global memory, may be nullptr
+  unsigned long long limit_ns;    // how long a wait may last before it gives up
 
   __device__ __forceinline__ bool aborted() const { return *abort_flag != 0; }
 
@@ -139,7 +131,7 @@ struct Watchdog {
         const unsigned long long now = global_timer_ns();
         if (t0 == 0) {
           t0 = now;
-        } else if (now - t0 > kWaitLimitNs) {
+        } else if (now - t0 > limit_ns) {
           give_up(site);
           return false;
         }

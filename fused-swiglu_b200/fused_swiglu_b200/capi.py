@@ -49,6 +49,8 @@ SIGNATURES = {
     "fswiglu_reduce_bcast_bf16": (_int, [_vp, ctypes.POINTER(ctypes.c_void_p), _int, _i64, _i64, _int, _vp]),
     "fswiglu_set_max_ctas": (_int, [_int]),
     "fswiglu_device_status": (_int, [ctypes.POINTER(ctypes.c_uint32), _vp]),
+    "fswiglu_set_wait_limit_us": (_i64, [_i64]),
+    "fswiglu_test_expire_next_wait": (None, [_int]),
     "fswiglu_status_string": (ctypes.c_char_p, [_int]),
     "fswiglu_version": (ctypes.c_char_p, []),
     "fswiglu_launch_count": (ctypes.c_uint64, []),

@@ -239,6 +239,26 @@ int fswiglu_set_max_ctas(int max_ctas);
  */
 int fswiglu_device_status(uint32_t* status, void* stream);
 
+/*
+ * Limit, in microseconds, of every device-side wait in kernels launched from now on (process-wide;
+ * default 2 000 000; limit_us <= 0 restores the default).  Returns the previous limit.  A wait that runs
+ * out makes its kernel unwind (copies and tensor-core work in flight are drained, tensor memory is freed)
+ * and shows up in fswiglu_device_status().  No counterpart in the reference, whose kernel has no waits
+ * that can run out (csrc/SwiGLU/swiglu.cu:290-343 uses cp.async groups and __syncthreads).
+ */
+int64_t fswiglu_set_wait_limit_us(int64_t limit_us);
+
+/*
+ * Test aid for the time-out path, no counterpart in the reference.  After fswiglu_test_expire_next_wait(1)
+ * the NEXT kernel launch of this library (one launch, then the switch is off again) is made so that one of
+ * its bounded waits cannot be satisfied: the first CTA of a tiled GEMM leaves out one operand copy, the
+ * small-batch kernel expects one more CTA at its hand-over than exists.  Nothing faults, traps or spins
+ * without bound: the wait runs out after the limit above, the kernel unwinds and returns, the launch's
+ * output is undefined and fswiglu_device_status() reports FSWIGLU_ERR_WATCHDOG with the site of the wait.
+ * Use it with a limit of a few milliseconds.
+ */
+void fswiglu_test_expire_next_wait(int enable);
+
 /* Human-readable name of a status code returned by this library. */
 const char* fswiglu_status_string(int status);
 
