@@ -281,11 +281,11 @@ def kernel_name(M, n_out, tile, sms, gated):
 def tensor_roofline(name, rows, d, Fl, gateup_ms, n_launches, region_ms, sms, world, clocks=None):
     """Denominator: the measured cuBLAS bf16 peak of the regime the timed region ran in - the burst figure
     while the GPU still boosts, the sustained one once the 1 kW power cap sets the clock (a region of
-    half a second or more, or a median SM clock under 85 % of the maximum while it ran)."""
+    half a second or more, or a median SM clock under 75 % of the maximum while it ran)."""
     peaks, peak_src = measured_peaks()
     capped = False
     if clocks and clocks.get("sm_mhz") and clocks.get("sm_max_mhz"):
-        capped = clocks["sm_mhz"] < 0.85 * clocks["sm_max_mhz"]
+        capped = clocks["sm_mhz"] < 0.75 * clocks["sm_max_mhz"]
     sustained = region_ms >= 500.0 or capped
     peak = peaks["bf16_tflops_sustained"] if sustained else peaks["bf16_tflops"]
     flops = 4.0 * rows * d * Fl
@@ -490,10 +490,15 @@ def e2e_single(w, args):
         fsw.ops.fused_swiglu_mlp_bf16_host(x_host, w.wg, w.wu, w.wd, out_host, ws_host)
     torch.cuda.synchronize()
     s = (time.perf_counter() - t0) / e2e_steps
-    same = torch.equal(out_host, w.step(False).cpu())
+    # the host path works on 1024-row slabs, whose tiles are scheduled (and, in a split last wave, summed) differently
+    # from the one-launch device path: same rounding points, results equal to within a bf16 ulp on a few entries
+    dev_out = w.step(False).float()
+    torch.cuda.synchronize()
+    rel = float((out_host.to(w.dev).float() - dev_out).norm() / dev_out.norm())
+    assert rel <= 1e-3, f"host-buffer path and device path disagree: rel-Fro {rel}"
     return {"value": flops_mlp(M, d, F) / s / 1e12, "unit": UNIT, "h2d_bytes_per_step": M * d * 2,
             "d2h_bytes_per_step": M * d * 2, "ms_per_step": s * 1e3, "steps": e2e_steps,
-            "api": "fswiglu_mlp_bf16_host (row slabs pipelined over three streams)", "matches_device_path": bool(same)}
+            "api": "fswiglu_mlp_bf16_host (row slabs pipelined over three streams)", "rel_fro_vs_device_path": rel}
 
 
 def gpu_baselines(w, stream):

@@ -238,13 +238,42 @@ int check_matrix(const void* p, int64_t rows, int64_t cols, int64_t ld, bool tma
 // served from the 126 MB L2, so DRAM traffic = |A| + |B| * groups: use as few groups as an
 // 80 MB slab budget allows, of equal size.
 int pick_group_m(int num_m_tiles, int64_t K) {
-  const int64_t slab_budget = 80ll << 20;
+  int64_t slab_budget = 80ll << 20;
+  if (const char* env = std::getenv("FSWIGLU_SLAB_MB")) {  // experiments only
+    const int v = std::atoi(env);
+    if (v >= 1 && v <= 4096) slab_budget = static_cast<int64_t>(v) << 20;
+  }
   int64_t g = slab_budget / (128 * K * 2);
   if (g < 1) g = 1;
   if (g > num_m_tiles) g = num_m_tiles;
   const int64_t groups = (num_m_tiles + g - 1) / g;
   g = (num_m_tiles + groups - 1) / groups;
   return static_cast<int>(g);
+}
+
+// Raster of the two-SM kernel: how many 256-row M-tiles share a sweep over N.  The clusters that run at
+// the same time work on group_m M-tiles x (clusters / group_m) N-tiles, and what they read from HBM is
+// decided by what the L2 keeps between their reads.  Measured on B200 (DRAM counters and sustained rates at
+// the 7B, 70B, 70B-shard and ragged-13B-shard shapes): operands shared by all SMs are kept in both halves of
+// the L2, so only about 50 MB of such data stay resident, and a full-K operand row of one tile is large
+// (256 rows x K x 2 bytes: 4 MB at K = 8192).
+//   * B small enough to stay resident: a wave should span all N-tiles, so that every A row is read once;
+//   * A small enough to stay resident: one group, every wave re-uses the same A rows;
+//   * neither: the most compact wave, group_m ~ sqrt(clusters), which minimises the distinct operand rows
+//     per wave (nothing survives from one wave to the next anyway).
+int pick_pair_group_m(int num_m_tiles, int num_n_tiles, int64_t K, int clusters) {
+  const int64_t row_bytes = 256 * K * 2;  // one M-tile of A, or one N-tile of B (256 operand rows in every mode)
+  const int64_t resident = 48ll << 20;
+  int g;
+  if (num_n_tiles * row_bytes <= resident) {
+    g = (clusters + num_n_tiles - 1) / num_n_tiles;
+  } else if (num_m_tiles * row_bytes <= resident) {
+    g = num_m_tiles;
+  } else {
+    g = 1;
+    while ((g + 1) * (g + 1) <= clusters) ++g;  // floor(sqrt(clusters)): 8 for 74 clusters
+  }
+  return std::max(1, std::min(g, num_m_tiles));
 }
 
 // Width of a tile in output columns.  Measured on B200, a tile's main loop is bound by the
@@ -385,8 +414,15 @@ int launch_gemm_pair(const DeviceState& st, const void* a, int64_t lda, const vo
   p.tile_n = (kMode == kPlain) ? 256 : 128;
   p.num_m_tiles = (p.M + 255) / 256;
   p.num_n_tiles = (p.n_out + p.tile_n - 1) / p.tile_n;
-  p.group_m = pick_group_m(2 * p.num_m_tiles, p.K) / 2;
-  if (p.group_m < 1) p.group_m = 1;
+  const int pairs = p.num_m_tiles * p.num_n_tiles;
+  const int clusters = std::max(1, std::min(pairs, effective_ctas(st) / 2));
+  p.group_m = pick_pair_group_m(p.num_m_tiles, p.num_n_tiles, p.K, clusters);
+  if (const char* env = std::getenv("FSWIGLU_GROUP_M")) {  // experiments only
+    const int v = std::atoi(env);
+    if (v >= 1) p.group_m = std::min(v, p.num_m_tiles);
+  }
+  if (const char* env = std::getenv("FSWIGLU_HINT_A")) p.hint_a = std::atoi(env);
+  if (const char* env = std::getenv("FSWIGLU_HINT_B")) p.hint_b = std::atoi(env);
   p.split_from = p.num_m_tiles * p.num_n_tiles;
   p.half_boxes = 0;
   int rc;
@@ -395,8 +431,6 @@ int launch_gemm_pair(const DeviceState& st, const void* a, int64_t lda, const vo
   if ((rc = encode_map(&mb0, b0, b_rows, p.K, ldb, 128))) return rc;
   mb1 = mb0;
   if (b1 != nullptr && (rc = encode_map(&mb1, b1, b_rows, p.K, ldb, 128))) return rc;
-  const int pairs = p.num_m_tiles * p.num_n_tiles;
-  const int clusters = std::max(1, std::min(pairs, effective_ctas(st) / 2));
   plan_pair_tail(&p, clusters, (p.K + kBlockK - 1) / kBlockK, scratch);
   if (p.tail_len > 0 && !scratch.counters_clean) {
     if (cudaMemsetAsync(p.tail_counters, 0, kTailCounterBytes, stream) != cudaSuccess) return FSWIGLU_ERR_CUDA;

@@ -113,6 +113,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       PairSchedule sched(p.num_m_tiles * p.num_n_tiles, p.tail_first, p.tail_len, cluster_id, num_clusters, num_kb);
       PairUnit un;
       bool withhold = p.withhold_one_copy != 0 && blockIdx.x == 0;  // one-shot, leader of the first pair
+      const uint64_t pol_a = l2_policy_of(p.hint_a), pol_b = l2_policy_of(p.hint_b);
       while (alive && sched.next(&un)) {
         const TileCoord tc = tile_coord(un.tile, p);
         const int m0 = tc.m_tile * 256 + static_cast<int>(rank) * 128;
@@ -136,8 +137,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           // one barrier per stage, in the leader: it expects the bytes of both CTAs' halves
           if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2u * stage_tx_bytes);
           const uint32_t leader_full = map_to_cta(full_bar(stage), 0);
-          tma_load_2d_pair(a_dst, &map_a, leader_full, kb * kBlockK, m0);
-          if (!withhold) tma_load_2d_pair(a_dst + kATileBytes, bmap, leader_full, kb * kBlockK, b_row);
+          tma_load_2d_pair_hint(a_dst, &map_a, leader_full, kb * kBlockK, m0, pol_a);
+          if (!withhold) tma_load_2d_pair_hint(a_dst + kATileBytes, bmap, leader_full, kb * kBlockK, b_row, pol_b);
           withhold = false;
           issued_mask |= 1u << stage;
           last_parity_mask = (last_parity_mask & ~(1u << stage)) | (phase << stage);

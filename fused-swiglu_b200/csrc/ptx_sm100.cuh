@@ -169,6 +169,16 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst_smem, const CUtens
       : "memory");
 }
 
+// Pair variant with an L2 eviction-priority hint.
+__device__ __forceinline__ void tma_load_2d_pair_hint(uint32_t dst_smem, const CUtensorMap* map, uint32_t cluster_bar,
+                                                      int32_t x, int32_t y, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(x), "r"(y), "l"(policy)
+      : "memory");
+}
+
 // Same, with an L2 eviction-priority hint.
 __device__ __forceinline__ void tma_load_2d_hint(uint32_t dst_smem, const CUtensorMap* map,
                                                  uint32_t bar, int32_t x, int32_t y,
@@ -197,6 +207,16 @@ __device__ __forceinline__ uint64_t l2_policy_evict_last() {
   uint64_t p;
   asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
   return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_normal() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+// Operand residency classes of the tiled GEMMs: 0 = default, 1 = streamed (evict first), 2 = kept (evict last).
+enum L2Hint : int { kL2Default = 0, kL2Stream = 1, kL2Keep = 2 };
+__device__ __forceinline__ uint64_t l2_policy_of(int hint) {
+  return hint == kL2Stream ? l2_policy_evict_first() : (hint == kL2Keep ? l2_policy_evict_last() : l2_policy_evict_normal());
 }
 
 // ------------------------------ tcgen05 ------------------------------------

@@ -91,11 +91,12 @@ def _timeline_us(rows_list, d, F_local, world, ctas) -> float:
 
 
 def plan_slabs(M: int, d: int, F_local: int, world: int, ctas: int) -> list:
-    """Slab heights (rows) for the push mode: all but the last a multiple of 128 (hence of 8 * world)."""
+    """Slab heights (rows) for the push mode: all but the last a multiple of 256 (the row count of a two-SM
+    tile, hence also of 8 * world)."""
     if M <= 1024 or world == 1:
         return [M]
     best_rows, best_t = [M], _timeline_us([M], d, F_local, world, ctas)
-    for R in range(256, M, 128):
+    for R in range(256, M, 256):
         n = -(-M // R)
         if n > 8:
             continue

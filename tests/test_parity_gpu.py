@@ -172,9 +172,21 @@ def test_full_size_configs_row_subset(fsw, cuda_dev, name):
     out2 = fsw.ops.fused_swiglu_mlp_bf16(xd, wgd, wud, wdd)
     assert torch.equal(out, out2), "not deterministic"
     if x.size(0) >= 256:
+        # A row's result must not depend on where the row sits in the batch.  Bit for bit when every tile
+        # is reduced in one piece; with the split last wave (default) a row that lands in one of the shared
+        # tiles is summed in a different order, so there the comparison is within the same-rounding tolerance.
         perm = torch.randperm(x.size(0), generator=torch.Generator().manual_seed(1)).to(cuda_dev)
-        out_p = fsw.ops.fused_swiglu_mlp_bf16(xd[perm].contiguous(), wgd, wud, wdd)
-        assert torch.equal(out_p, out[perm]), "rows are not independent of their position"
+        xp = xd[perm].contiguous()
+        out_p = fsw.ops.fused_swiglu_mlp_bf16(xp, wgd, wud, wdd)
+        m = orc.error_metrics(f32(out_p), f32(out[perm]))
+        assert m["rel_fro"] <= REL_FRO_SAME_ROUNDING and m["scaled_max_abs"] <= 2.0 ** -7, m
+        os.environ["FSWIGLU_TAIL_SPLITK"] = "0"
+        try:
+            a = fsw.ops.fused_swiglu_mlp_bf16(xd, wgd, wud, wdd)
+            b = fsw.ops.fused_swiglu_mlp_bf16(xp, wgd, wud, wdd)
+        finally:
+            del os.environ["FSWIGLU_TAIL_SPLITK"]
+        assert torch.equal(b, a[perm]), "rows are not independent of their position"
     out_neg = fsw.ops.fused_swiglu_mlp_bf16(xd, wgd, wud, (-wdd).contiguous())
     assert torch.equal(out_neg, -out), "not odd in W_down"
     out_scaled = fsw.ops.fused_swiglu_mlp_bf16(xd, wgd, wud, (wdd * 2).contiguous())
@@ -343,7 +355,7 @@ def test_push_reduction_kernels_on_one_gpu(fsw, cuda_dev, world, M, d, F):
         g, u, dn = (t.to(cuda_dev) for t in fsw.pack.shard_mlp_weights(wg, wu, wd, world, r))
         h = fsw.ops.fused_swiglu_gateup_bf16(xd, g, u)
         rc = lib.fswiglu_down_scatter_bf16(ctypes.c_void_p(h.data_ptr()), h.size(1), ctypes.c_void_p(dn.data_ptr()),
-                                           dn.size(1), recv_ptrs, world, r, rpo, M, d, h.size(1), None)
+                                           dn.size(1), recv_ptrs, world, r, rpo, M, d, h.size(1), None, 0, None)
         assert rc == capi.OK, capi.status_string(rc)
     torch.cuda.synchronize()
     for o in range(world):
@@ -358,7 +370,7 @@ def test_push_reduction_kernels_on_one_gpu(fsw, cuda_dev, world, M, d, F):
     # bf16 partials on the wire + fp32 accumulation + one rounding
     assert m["rel_fro"] <= REL_FRO_GRADED and m["scaled_max_abs"] <= SCALED_MAX_ABS, m
     # bad arguments are refused before anything is launched
-    assert lib.fswiglu_down_scatter_bf16(None, 8, None, 8, recv_ptrs, 9, 0, 8, 8, 8, 8, None) == capi.ERR_BAD_ARG
+    assert lib.fswiglu_down_scatter_bf16(None, 8, None, 8, recv_ptrs, 9, 0, 8, 8, 8, 8, None, 0, None) == capi.ERR_BAD_ARG
     assert lib.fswiglu_reduce_bcast_bf16(None, out_ptrs, 4, 0, 8, 0, None) == capi.OK
 
 
