@@ -59,8 +59,10 @@ def build_lib(force: bool = False, verbose: bool = False, ptxas_info: bool = Fal
     cmd = [nvcc, *NVCC_FLAGS]
     if ptxas_info:
         cmd += ["-Xptxas", "-v"]
-    cmd += ["-o", LIB] + [s for s in srcs if s.endswith(".cu")]
+    tmp = LIB + ".partial"
+    cmd += ["-o", tmp] + [s for s in srcs if s.endswith(".cu")]
     _run(cmd, verbose or ptxas_info)
+    os.replace(tmp, LIB)  # the library file is always a complete build
     return LIB
 
 
@@ -75,12 +77,13 @@ def build_ext(force: bool = False, verbose: bool = False) -> str:
     inc += ["-I/usr/local/cuda/include"]
     libdirs = cpp_extension.library_paths()
     cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-DTORCH_EXTENSION_NAME=fused_mlp_module",
-           "-DTORCH_API_INCLUDE_EXTENSION_H", *inc, src, "-o", EXT]
+           "-DTORCH_API_INCLUDE_EXTENSION_H", *inc, src, "-o", EXT + ".partial"]
     for d in libdirs:
         cmd += [f"-L{d}", f"-Wl,-rpath,{d}"]
     cmd += [f"-L{LIB_DIR}", "-Wl,-rpath,$ORIGIN/lib", "-lfswiglu", "-lc10", "-lc10_cuda", "-ltorch_cpu",
             "-ltorch_cuda", "-ltorch", "-ltorch_python"]
     _run(cmd, verbose)
+    os.replace(EXT + ".partial", EXT)
     return EXT
 
 

@@ -15,6 +15,7 @@
 
 #include "../../include/fswiglu.h"
 #include "decode_sm100.cuh"
+#include "elementwise_sm100.cuh"
 #include "gemm_pair_sm100.cuh"
 #include "gemm_sm100.cuh"
 
@@ -145,6 +146,7 @@ std::mutex g_mutex;
 DeviceState g_dev[kMaxDevices];
 std::atomic<uint64_t> g_launches{0};
 std::atomic<unsigned long long> g_wait_limit_ns{kWaitLimitNs};
+std::atomic<unsigned long long*> g_decode_trace{nullptr};  // profiling aid, see fswiglu_set_decode_trace
 std::atomic<int> g_withhold_one_copy{0};  // test aid, consumed by the next launch (see fswiglu_test_expire_next_wait)
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -593,6 +595,14 @@ int decode_impl(DeviceState& st, const void* x, int64_t ldx, const void* w_gate,
   p.M = static_cast<int>(M);
   p.n_pad = n_pad;
   p.prefetch_units = decode_prefetch_units();
+  // more token-tile slots for wide token tiles: 64 tokens are 8 KiB per k-block, and four of them would be
+  // only two microseconds of look-ahead
+  p.w_slots = n_pad >= 64 ? kDecWSlots - 2 : (n_pad >= 32 ? kDecWSlots - 1 : kDecWSlots);
+  if (const char* env = std::getenv("FSWIGLU_DECODE_WSLOTS")) {  // experiments only
+    const int v = std::atoi(env);
+    if (v >= 4 && v <= kDecWSlots) p.w_slots = v;
+  }
+  p.trace = g_decode_trace.load(std::memory_order_relaxed);
   p.row_scale = fu.row_scale;
   p.residual = fu.residual;
   p.ld_res = fu.ld_res;
@@ -943,6 +953,148 @@ int fswiglu_static_status(uint32_t* status, void* stream) {
   return word == 0 ? FSWIGLU_OK : FSWIGLU_ERR_WATCHDOG;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Backward pass: seven K-major tensor-core GEMMs (the plain mode of the forward kernels) plus two
+// bandwidth-bound kernels that produce their operands (elementwise_sm100.cuh).
+// ---------------------------------------------------------------------------------------------
+int fswiglu_gemm_tn_bf16(const void* a, int64_t lda, const void* b, int64_t ldb, void* c, int64_t ldc, int64_t M,
+                         int64_t N, int64_t K, int out_dtype, void* scratch, size_t scratch_bytes, void* stream) {
+  // C [M, N] = A [M, K] B [N, K]^T: exactly the down projection with (h, W_down, out, d, F) = (A, B, C, N, K)
+  return fswiglu_down_bf16_ex(a, lda, b, ldb, c, ldc, M, N, K, out_dtype, nullptr, 0, scratch, scratch_bytes, stream);
+}
+
+namespace {
+
+int ew_grid(const DeviceState& st, int64_t tiles) {
+  const int64_t cap = static_cast<int64_t>(st.num_sms) * 8;
+  return static_cast<int>(std::max<int64_t>(1, std::min(tiles, cap)));
+}
+
+int transpose_impl(DeviceState& st, const void* src, int64_t ld_src, void* dst, int64_t ld_dst, int64_t rows,
+                   int64_t cols, cudaStream_t s) {
+  if (rows == 0 || cols == 0) return FSWIGLU_OK;
+  const int64_t dst_cols = (rows + 7) / 8 * 8;
+  if (src == nullptr || dst == nullptr) return FSWIGLU_ERR_BAD_ARG;
+  if (rows > 0x7fffffffll || cols > 0x7fffffffll) return FSWIGLU_ERR_SHAPE;
+  if (cols % 8 != 0 || ld_src < cols || ld_dst < dst_cols) return FSWIGLU_ERR_SHAPE;
+  if (!aligned16(src) || !aligned16(dst) || ld_src % 8 != 0 || ld_dst % 8 != 0) return FSWIGLU_ERR_ALIGNMENT;
+  const int64_t tiles = ((dst_cols + kEwTile - 1) / kEwTile) * ((cols + kEwTile - 1) / kEwTile);
+  transpose_bf16_kernel<<<ew_grid(st, tiles), kEwThreads, 0, s>>>(
+      static_cast<const __nv_bfloat16*>(src), ld_src, static_cast<__nv_bfloat16*>(dst), ld_dst, static_cast<int>(rows),
+      static_cast<int>(cols), static_cast<int>(dst_cols));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
+}
+
+struct BackwardLayout {
+  size_t g, u, dh, dgdu, dgT, duT, hT, doutT, xT, wdT, wguT, scratch, total;
+  int64_t Mp;
+};
+
+BackwardLayout backward_layout(int64_t M, int64_t d, int64_t F) {
+  BackwardLayout L = {};
+  L.Mp = (M + 7) / 8 * 8;
+  size_t off = 0;
+  auto take = [&](size_t elems) {
+    const size_t at = off;
+    off += round_up(elems * 2u, 256);
+    return at;
+  };
+  const size_t MF = static_cast<size_t>(M) * F, FMp = static_cast<size_t>(F) * L.Mp, dMp = static_cast<size_t>(d) * L.Mp;
+  L.g = take(MF);
+  L.u = take(MF);
+  L.dh = take(MF);
+  L.dgdu = take(2 * MF);
+  L.dgT = take(FMp);
+  L.duT = take(FMp);
+  L.hT = take(FMp);
+  L.doutT = take(dMp);
+  L.xT = take(dMp);
+  L.wdT = take(static_cast<size_t>(F) * d);
+  L.wguT = take(2 * static_cast<size_t>(d) * F);
+  L.scratch = off;
+  off += kTailScratchBytes;
+  L.total = off;
+  return L;
+}
+
+}  // namespace
+
+int fswiglu_transpose_bf16(const void* src, int64_t ld_src, void* dst, int64_t ld_dst, int64_t rows, int64_t cols,
+                           void* stream) {
+  if (rows < 0 || cols < 0) return FSWIGLU_ERR_BAD_ARG;
+  DeviceState* st = nullptr;
+  if (int rc = device_state(&st)) return rc;
+  return transpose_impl(*st, src, ld_src, dst, ld_dst, rows, cols, static_cast<cudaStream_t>(stream));
+}
+
+size_t fswiglu_backward_workspace_bytes(int64_t M, int64_t d, int64_t F) {
+  if (M <= 0 || d <= 0 || F <= 0) return 0;
+  return backward_layout(M, d, F).total;
+}
+
+int fswiglu_mlp_backward_bf16(const void* x, int64_t ldx, const void* w_gate, const void* w_up, int64_t ldw_gu,
+                              const void* w_down, int64_t ldw_d, const void* dout, int64_t ld_dout, void* dx,
+                              int64_t ld_dx, void* d_w_gate, void* d_w_up, int64_t ld_dw_gu, void* d_w_down,
+                              int64_t ld_dw_d, int grad_dtype, int64_t M, int64_t d, int64_t F, void* workspace,
+                              size_t workspace_bytes, void* stream) {
+  if (M < 0 || F <= 0 || d <= 0) return FSWIGLU_ERR_BAD_ARG;
+  if (grad_dtype != FSWIGLU_OUT_BF16 && grad_dtype != FSWIGLU_OUT_F32) return FSWIGLU_ERR_BAD_ARG;
+  if (M == 0) return FSWIGLU_OK;  // no tokens: the caller's weight gradients are zero, nothing is written
+  if (d % 8 != 0 || F % 8 != 0) return FSWIGLU_ERR_SHAPE;
+  DeviceState* st = nullptr;
+  if (int rc = device_state(&st)) return rc;
+  const BackwardLayout L = backward_layout(M, d, F);
+  if (workspace == nullptr || workspace_bytes < L.total || (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
+    return FSWIGLU_ERR_WORKSPACE;
+  int rc;
+  if ((rc = check_matrix(x, M, d, ldx, true))) return rc;
+  if ((rc = check_matrix(dout, M, d, ld_dout, true))) return rc;
+  if ((rc = check_matrix(w_gate, F, d, ldw_gu, true))) return rc;
+  if ((rc = check_matrix(w_up, F, d, ldw_gu, true))) return rc;
+  if ((rc = check_matrix(w_down, d, F, ldw_d, true))) return rc;
+  if (dx == nullptr || d_w_gate == nullptr || d_w_up == nullptr || d_w_down == nullptr) return FSWIGLU_ERR_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  auto at = [&](size_t off) { return static_cast<void*>(ws + off); };
+  void* scratch = at(L.scratch);
+  const size_t sb = kTailScratchBytes;
+  const int bf = FSWIGLU_OUT_BF16;
+  // 1. recompute the pre-activations (the forward keeps only x): g = x Wg^T, u = x Wu^T
+  if ((rc = fswiglu_gemm_tn_bf16(x, ldx, w_gate, ldw_gu, at(L.g), F, M, F, d, bf, scratch, sb, stream))) return rc;
+  if ((rc = fswiglu_gemm_tn_bf16(x, ldx, w_up, ldw_gu, at(L.u), F, M, F, d, bf, scratch, sb, stream))) return rc;
+  // 2. dh = dout Wd  (B operand K-major: Wd^T [F, d])
+  if ((rc = transpose_impl(*st, w_down, ldw_d, at(L.wdT), d, d, F, s))) return rc;
+  if ((rc = fswiglu_gemm_tn_bf16(dout, ld_dout, at(L.wdT), d, at(L.dh), F, M, F, d, bf, scratch, sb, stream))) return rc;
+  // 3. gate derivative, with the transposes the weight-gradient products need
+  {
+    const int64_t tiles = ((L.Mp + kEwTile - 1) / kEwTile) * ((F + kEwTile - 1) / kEwTile);
+    swiglu_bwd_kernel<<<ew_grid(*st, tiles), kEwThreads, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(at(L.g)), static_cast<const __nv_bfloat16*>(at(L.u)),
+        static_cast<const __nv_bfloat16*>(at(L.dh)), F, static_cast<__nv_bfloat16*>(at(L.dgdu)), 2 * F,
+        static_cast<__nv_bfloat16*>(at(L.dgT)), static_cast<__nv_bfloat16*>(at(L.duT)),
+        static_cast<__nv_bfloat16*>(at(L.hT)), L.Mp, static_cast<int>(M), static_cast<int>(F), static_cast<int>(L.Mp));
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (cudaGetLastError() != cudaSuccess) return FSWIGLU_ERR_CUDA;
+  }
+  // 4. weight gradients, contracting over the (padded) token dimension
+  if ((rc = transpose_impl(*st, dout, ld_dout, at(L.doutT), L.Mp, M, d, s))) return rc;
+  if ((rc = transpose_impl(*st, x, ldx, at(L.xT), L.Mp, M, d, s))) return rc;
+  if ((rc = fswiglu_gemm_tn_bf16(at(L.doutT), L.Mp, at(L.hT), L.Mp, d_w_down, ld_dw_d, d, F, L.Mp, grad_dtype, scratch, sb,
+                                 stream)))
+    return rc;
+  if ((rc = fswiglu_gemm_tn_bf16(at(L.dgT), L.Mp, at(L.xT), L.Mp, d_w_gate, ld_dw_gu, F, d, L.Mp, grad_dtype, scratch, sb,
+                                 stream)))
+    return rc;
+  if ((rc = fswiglu_gemm_tn_bf16(at(L.duT), L.Mp, at(L.xT), L.Mp, d_w_up, ld_dw_gu, F, d, L.Mp, grad_dtype, scratch, sb,
+                                 stream)))
+    return rc;
+  // 5. dx = [dg | du] [Wg; Wu]: one product over K = 2F with B = [Wg^T | Wu^T] [d, 2F]
+  if ((rc = transpose_impl(*st, w_gate, ldw_gu, at(L.wguT), 2 * F, F, d, s))) return rc;
+  if ((rc = transpose_impl(*st, w_up, ldw_gu, static_cast<__nv_bfloat16*>(at(L.wguT)) + F, 2 * F, F, d, s))) return rc;
+  return fswiglu_gemm_tn_bf16(at(L.dgdu), 2 * F, at(L.wguT), 2 * F, dx, ld_dx, M, d, 2 * F, grad_dtype, scratch, sb, stream);
+}
+
 int fswiglu_cast_f32_to_bf16(const void* src, void* dst, int64_t n, void* stream) {
   if (n < 0 || (n > 0 && (src == nullptr || dst == nullptr))) return FSWIGLU_ERR_BAD_ARG;
   if (n == 0) return FSWIGLU_OK;
@@ -1047,6 +1199,10 @@ int fswiglu_set_max_ctas(int max_ctas) {
 int64_t fswiglu_set_wait_limit_us(int64_t limit_us) {
   const unsigned long long ns = limit_us > 0 ? static_cast<unsigned long long>(limit_us) * 1000ull : kWaitLimitNs;
   return static_cast<int64_t>(g_wait_limit_ns.exchange(ns, std::memory_order_relaxed) / 1000ull);
+}
+
+void fswiglu_set_decode_trace(void* device_buffer) {
+  g_decode_trace.store(static_cast<unsigned long long*>(device_buffer), std::memory_order_relaxed);
 }
 
 void fswiglu_test_expire_next_wait(int enable) { g_withhold_one_copy.store(enable != 0 ? 1 : 0, std::memory_order_relaxed); }

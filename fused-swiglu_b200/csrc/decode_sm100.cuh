@@ -80,6 +80,14 @@ struct DecodeParams {
   unsigned long long wait_limit_ns;  // limit of every device-side wait in this launch
   unsigned int handover_target;      // CTAs that must have finished phase 1 (= the grid size; tests of the
                                      // time-out path pass one more, which nothing ever reaches)
+  int w_slots;                       // weight-tile slots in use (<= kDecWSlots); the token-tile ring takes the rest
+  unsigned long long* trace;         // optional: kDecTraceStamps %globaltimer stamps per CTA (profiling aid)
+};
+
+// Time stamps a CTA leaves in DecodeParams::trace (one 64-bit slot each, 0 = not reached).
+enum DecodeStamp : int {
+  kStampSetupDone = 0, kStampP1FirstTile, kStampP1MmasIssued, kStampP1HandoverSignalled, kStampP2FirstTile,
+  kStampP2MmasIssued, kStampP2EpilogueDone, kStampHandoverObserved, kDecTraceStamps
 };
 
 // First unit of CTA c when `units` units are cut into `ctas` contiguous ranges.
@@ -106,9 +114,15 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
                     const __grid_constant__ CUtensorMap map_h, const DecodeParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  // ring area: w_slots weight slots of 16 KiB, then the token-tile ring in what is left of the
+  // (kDecWSlots * 16 KiB + 32 KiB) area; the barrier block follows at a fixed offset
+  const int w_slots = p.w_slots;
   const uint32_t w_ring = smem_base;
-  const uint32_t x_ring = smem_base + kDecWSlots * kDecWSlotBytes;
-  const uint32_t bar_base = x_ring + kDecXRingBytes;
+  const uint32_t x_ring = smem_base + static_cast<uint32_t>(w_slots) * kDecWSlotBytes;
+  const uint32_t bar_base = smem_base + kDecWSlots * kDecWSlotBytes + kDecXRingBytes;
+  auto stamp = [&](int which) {
+    if (p.trace != nullptr) p.trace[static_cast<size_t>(blockIdx.x) * kDecTraceStamps + which] = global_timer_ns();
+  };
   auto w_full = [&](int s) { return bar_base + 8u * s; };
   auto w_empty = [&](int s) { return bar_base + 8u * (kDecWSlots + s); };
   auto x_full = [&](int s) { return bar_base + 8u * (2 * kDecWSlots + s); };
@@ -130,7 +144,8 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
 
   constexpr int kAccStride = 128;  // TMEM columns per accumulator stage (2 stages)
   const uint32_t x_slot_bytes = static_cast<uint32_t>(p.n_pad) * 128u;
-  const int x_slots = kDecXRingBytes / static_cast<int>(x_slot_bytes);  // 16 / 8 / 4
+  const int x_slots = min(kDecMaxXSlots, (kDecXRingBytes + (kDecWSlots - w_slots) * kDecWSlotBytes) /
+                                              static_cast<int>(x_slot_bytes));
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kDecWSlots; ++s) {
@@ -163,6 +178,7 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr_slot;
+  if (threadIdx.x == 0) stamp(kStampSetupDone);
 
   // phase 1: first weight row of this CTA's i-th tile (>= F: the tile does not exist)
   auto tile_row0 = [&](int i) {
@@ -187,7 +203,7 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
         tma_load_2d_hint(w_ring + slot * kDecWSlotBytes, map, w_full(slot), x, y, stream_once);
         issued_mask |= 1u << slot;
         last_parity_mask = (last_parity_mask & ~(1u << slot)) | (phase << slot);
-        if (++slot == kDecWSlots) {
+        if (++slot == w_slots) {
           slot = 0;
           phase ^= 1u;
         }
@@ -207,9 +223,9 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
       // are pulled into L2 a bounded distance ahead of the ring (fire and forget), and the ring's own
       // loads then hit L2.  The window is bounded because everything prefetched has to stay in L2
       // until it is used.
-      long long pf = u_begin + kDecWSlots;
+      long long pf = u_begin + w_slots;
       for (long long u = u_begin; u < u_end && alive; ++u) {
-        for (; pf < u_end && pf < u + kDecWSlots + p.prefetch_units; ++pf) {
+        for (; pf < u_end && pf < u + w_slots + p.prefetch_units; ++pf) {
           const int prb = static_cast<int>(pf / p.k_blocks2);
           const int pkb = static_cast<int>(pf - static_cast<long long>(prb) * p.k_blocks2);
           tma_prefetch_l2_2d(&map_down, pkb * 64, prb * 128);
@@ -219,7 +235,7 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
         alive = fill(&map_down, kb * 64, rb * 128, 128u * 128u);
       }
       if (wd.aborted()) {
-        for (int s = 0; s < kDecWSlots; ++s) {
+        for (int s = 0; s < w_slots; ++s) {
           if (issued_mask & (1u << s)) {
             const uint32_t par = (last_parity_mask >> s) & 1u;
             const unsigned long long t0 = global_timer_ns();
@@ -274,6 +290,7 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
         }
         // h was written with ordinary stores by other SMs; order them before this SM's TMA reads
         asm volatile("fence.proxy.async;" ::: "memory");
+        stamp(kStampHandoverObserved);
       }
       for (long long u = u_begin; u < u_end && alive; ++u) {
         alive = push(&map_h, static_cast<int>(u % p.k_blocks2));
@@ -303,7 +320,7 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
       uint32_t acc_phase = 0;
       bool alive = true;
       auto next_w = [&]() {
-        if (++ws == kDecWSlots) {
+        if (++ws == w_slots) {
           ws = 0;
           wphase ^= 1u;
         }
@@ -337,6 +354,7 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
           }
           next_w();
           tc_fence_after_sync();
+          if (i == 0 && kb == 0) stamp(kStampP1FirstTile);
           const uint64_t g_desc = umma_desc_k_sw128(w_ring + w0 * kDecWSlotBytes);
           const uint64_t u_desc = umma_desc_k_sw128(w_ring + w1 * kDecWSlotBytes);
           const uint64_t x_desc = umma_desc_k_sw128(x_ring + xs * x_slot_bytes);
@@ -356,6 +374,7 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
+      if (alive) stamp(kStampP1MmasIssued);
       // ---- phase 2: one accumulator per (row-block, k-range) segment ----
       long long u = u_begin;
       while (u < u_end && alive) {
@@ -374,6 +393,7 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
             break;
           }
           tc_fence_after_sync();
+          if (u == u_begin) stamp(kStampP2FirstTile);
           const uint64_t w_desc = umma_desc_k_sw128(w_ring + ws * kDecWSlotBytes);
           const uint64_t x_desc = umma_desc_k_sw128(x_ring + xs * x_slot_bytes);
 #pragma unroll
@@ -391,6 +411,7 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
+      if (alive) stamp(kStampP2MmasIssued);
       if (wd.aborted()) {
         umma_commit(drain_bar);
         const unsigned long long t0 = global_timer_ns();
@@ -466,6 +487,7 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
     asm volatile("bar.sync 1, 128;" ::: "memory");
     if (epi_tid == 0 && alive) {
       asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.handover) : "memory");
+      stamp(kStampP1HandoverSignalled);
     }
 
     // ---- phase 2: segments of row-blocks, combined through fp32 partial tiles ----
@@ -562,6 +584,7 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
       }
       if (nseg == 1) release_accumulator();
     }
+    if (epi_tid == 0 && alive) stamp(kStampP2EpilogueDone);
   }
 
   tc_fence_before_sync();

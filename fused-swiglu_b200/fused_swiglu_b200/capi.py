@@ -43,6 +43,11 @@ SIGNATURES = {
     "fswiglu_mlp_bf16_host": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _sz, _vp]),
     "fswiglu_host_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "fswiglu_mlp_bf16_static": (_int, [_vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _int, _i64, _i64, _i64, _vp]),
+    "fswiglu_backward_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "fswiglu_mlp_backward_bf16": (_int, [_vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _vp,
+                                         _i64, _int, _i64, _i64, _i64, _vp, _sz, _vp]),
+    "fswiglu_gemm_tn_bf16": (_int, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
+    "fswiglu_transpose_bf16": (_int, [_vp, _i64, _vp, _i64, _i64, _i64, _vp]),
     "fswiglu_cast_f32_to_bf16": (_int, [_vp, _vp, _i64, _vp]),
     "fswiglu_down_scatter_bf16": (_int, [_vp, _i64, _vp, _i64, ctypes.POINTER(ctypes.c_void_p), _int, _int, _i64, _i64,
                                          _i64, _i64, _vp, _sz, _vp]),
@@ -51,6 +56,7 @@ SIGNATURES = {
     "fswiglu_device_status": (_int, [ctypes.POINTER(ctypes.c_uint32), _vp]),
     "fswiglu_set_wait_limit_us": (_i64, [_i64]),
     "fswiglu_test_expire_next_wait": (None, [_int]),
+    "fswiglu_set_decode_trace": (None, [_vp]),
     "fswiglu_status_string": (ctypes.c_char_p, [_int]),
     "fswiglu_version": (ctypes.c_char_p, []),
     "fswiglu_launch_count": (ctypes.c_uint64, []),

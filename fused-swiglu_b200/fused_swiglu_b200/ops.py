@@ -216,3 +216,80 @@ def fused_swiglu_mlp_bf16_host(x_host: torch.Tensor, W_gate: torch.Tensor, W_up:
                                             _vp(workspace), workspace.numel(),
                                             ctypes.c_void_p(_stream_ptr(W_gate)))
     capi.check(rc, "fused_swiglu_mlp_bf16_host")
+
+
+def gemm_tn_bf16(a: torch.Tensor, b: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
+                 scratch: torch.Tensor | None = None) -> torch.Tensor:
+    """c[M, N] = a[M, K] b[N, K]^T, both operands K-major bf16, fp32 accumulation (the GEMM of the backward pass)."""
+    _require_bf16_cuda(a=a, b=b)
+    if a.size(1) != b.size(1):
+        raise RuntimeError("a and b must share their last dimension")
+    return swiglu_down_bf16(a, b, out_dtype=out_dtype, scratch=scratch)
+
+
+def transpose_bf16(src: torch.Tensor) -> torch.Tensor:
+    """[rows, cols] -> [cols, rows rounded up to a multiple of 8], pad columns zero (a K-major GEMM operand)."""
+    _require_bf16_cuda(src=src)
+    rows, cols = src.shape
+    dst = torch.empty((cols, (rows + 7) // 8 * 8), dtype=torch.bfloat16, device=src.device)
+    with torch.cuda.device(src.device):
+        rc = capi.lib.fswiglu_transpose_bf16(_vp(src), _row_major_ld("src", src), _vp(dst), dst.stride(0), rows, cols,
+                                             ctypes.c_void_p(_stream_ptr(src)))
+    capi.check(rc, "transpose_bf16")
+    return dst
+
+
+def backward_workspace(M: int, d: int, F: int, device: torch.device | str | int) -> torch.Tensor:
+    return torch.empty(max(int(capi.lib.fswiglu_backward_workspace_bytes(M, d, F)), 256), dtype=torch.uint8, device=device)
+
+
+def swiglu_mlp_backward(x: torch.Tensor, W_gate: torch.Tensor, W_up: torch.Tensor, W_down: torch.Tensor,
+                        dout: torch.Tensor, grad_dtype: torch.dtype = torch.bfloat16,
+                        workspace: torch.Tensor | None = None):
+    """Gradients (dx, dW_gate, dW_up, dW_down) of out = (silu(x Wg^T) * (x Wu^T)) Wd^T for upstream dout [M, d]."""
+    _require_bf16_cuda(x=x, W_gate=W_gate, W_up=W_up, W_down=W_down, dout=dout)
+    M, d = x.shape
+    F = W_gate.size(0)
+    if W_up.shape != W_gate.shape or W_gate.size(1) != d or tuple(W_down.shape) != (d, F) or tuple(dout.shape) != (M, d):
+        raise RuntimeError("expected W_gate/W_up [F, d], W_down [d, F] and dout [M, d]")
+    if grad_dtype not in (torch.bfloat16, torch.float32):
+        raise RuntimeError("grad_dtype must be bfloat16 or float32")
+    ldw = _row_major_ld("W_gate", W_gate)
+    if _row_major_ld("W_up", W_up) != ldw:
+        raise RuntimeError("W_gate and W_up must share one leading dimension")
+    kw = dict(dtype=grad_dtype, device=x.device)
+    dx, dwg, dwu, dwd = (torch.empty((M, d), **kw), torch.empty((F, d), **kw), torch.empty((F, d), **kw),
+                         torch.empty((d, F), **kw))
+    if M == 0:
+        return dx, dwg.zero_(), dwu.zero_(), dwd.zero_()
+    if workspace is None:
+        workspace = backward_workspace(M, d, F, x.device)
+    code = capi.OUT_BF16 if grad_dtype == torch.bfloat16 else capi.OUT_F32
+    with torch.cuda.device(x.device):
+        rc = capi.lib.fswiglu_mlp_backward_bf16(_vp(x), _row_major_ld("x", x), _vp(W_gate), _vp(W_up), ldw, _vp(W_down),
+                                                _row_major_ld("W_down", W_down), _vp(dout), _row_major_ld("dout", dout),
+                                                _vp(dx), d, _vp(dwg), _vp(dwu), d, _vp(dwd), F, code, M, d, F,
+                                                _vp(workspace), workspace.numel(), ctypes.c_void_p(_stream_ptr(x)))
+    capi.check(rc, "swiglu_mlp_backward")
+    return dx, dwg, dwu, dwd
+
+
+class FusedSwiGLUMLPFunction(torch.autograd.Function):
+    """Differentiable form of the whole-MLP op: forward = the fused kernels, backward = swiglu_mlp_backward
+    (the pre-activations are recomputed there, so only the inputs are kept)."""
+
+    @staticmethod
+    def forward(ctx, x, W_gate, W_up, W_down):
+        ctx.save_for_backward(x, W_gate, W_up, W_down)
+        return fused_swiglu_mlp_bf16(x, W_gate, W_up, W_down)
+
+    @staticmethod
+    def backward(ctx, dout):
+        x, W_gate, W_up, W_down = ctx.saved_tensors
+        dx, dwg, dwu, dwd = swiglu_mlp_backward(x, W_gate, W_up, W_down, dout.contiguous().to(torch.bfloat16))
+        return dx, dwg, dwu, dwd
+
+
+def fused_swiglu_mlp(x: torch.Tensor, W_gate: torch.Tensor, W_up: torch.Tensor, W_down: torch.Tensor) -> torch.Tensor:
+    """Whole MLP with autograd support (bf16 CUDA tensors, 2-D x)."""
+    return FusedSwiGLUMLPFunction.apply(x, W_gate, W_up, W_down)

@@ -192,6 +192,37 @@ int fswiglu_mlp_bf16_static(const void* x, int64_t ldx, const void* w_gate, cons
 int fswiglu_static_status(uint32_t* status, void* stream);
 
 /*
+ * Backward pass of the MLP (no counterpart in the reference, which is forward only: its ops are named
+ * *_fwd and register no autograd, csrc/torch_bindings.cpp:38-50).  Given dout = dL/d out [M, d]:
+ *     g = x Wg^T, u = x Wu^T (recomputed), s = sigmoid(g), h = g s u
+ *     dh = dout Wd        dg = dh u s (1 + g (1 - s))        du = dh g s
+ *     dWd = dout^T h      dWg = dg^T x      dWu = du^T x      dx = dg Wg + du Wu
+ * Seven tensor-core GEMMs (the forward kernels' plain mode; operands that are not K-major are transposed
+ * first by a bandwidth-bound kernel) and one element-wise kernel; 16 M d F flops.  Intermediates are bf16,
+ * accumulation fp32.  dx [M, d], d_w_gate / d_w_up [F, d], d_w_down [d, F] are written (not accumulated)
+ * as bf16 or fp32 (grad_dtype).  The weight gradients contract over the token dimension, padded with
+ * zeros to a multiple of 8.  Gradients of the fused options (row_scale, residual) are not provided: the
+ * residual's is dout itself, the norm's belongs to the caller's norm.
+ */
+size_t fswiglu_backward_workspace_bytes(int64_t M, int64_t d, int64_t F);
+int fswiglu_mlp_backward_bf16(const void* x, int64_t ldx, const void* w_gate, const void* w_up, int64_t ldw_gu,
+                              const void* w_down, int64_t ldw_d, const void* dout, int64_t ld_dout, void* dx,
+                              int64_t ld_dx, void* d_w_gate, void* d_w_up, int64_t ld_dw_gu, void* d_w_down,
+                              int64_t ld_dw_d, int grad_dtype, int64_t M, int64_t d, int64_t F, void* workspace,
+                              size_t workspace_bytes, void* stream);
+
+/*
+ * The two building blocks of the backward pass, usable on their own (no counterpart in the reference):
+ * C [M, N] = A [M, K] B [N, K]^T with both operands K-major bf16 (fp32 accumulation; out_dtype and scratch
+ * as for fswiglu_down_bf16_ex, which this is), and dst [cols, rows rounded up to 8] = src [rows, cols]^T
+ * with zero padding (cols % 8 == 0, 16-byte aligned bases and pitches).
+ */
+int fswiglu_gemm_tn_bf16(const void* a, int64_t lda, const void* b, int64_t ldb, void* c, int64_t ldc, int64_t M,
+                         int64_t N, int64_t K, int out_dtype, void* scratch, size_t scratch_bytes, void* stream);
+int fswiglu_transpose_bf16(const void* src, int64_t ld_src, void* dst, int64_t ld_dst, int64_t rows, int64_t cols,
+                           void* stream);
+
+/*
  * dst[i] = bf16(src[i]) for n contiguous elements (round to nearest even): the single rounding after
  * tensor-parallel fp32 partial sums have been reduced.  No counterpart in the reference (single GPU).
  * src and dst must be 16-byte aligned.
@@ -258,6 +289,15 @@ int64_t fswiglu_set_wait_limit_us(int64_t limit_us);
  * Use it with a limit of a few milliseconds.
  */
 void fswiglu_test_expire_next_wait(int enable);
+
+/*
+ * Profiling aid for the small-batch kernel, no counterpart in the reference.  With a device buffer of
+ * (number of SMs) x 8 x 8 bytes set, every CTA of the small-batch kernel leaves eight %globaltimer stamps
+ * (nanoseconds) in it: set-up done, first phase-1 tile ready, phase-1 MMAs issued, hand-over signalled, first
+ * phase-2 tile ready, phase-2 MMAs issued, phase-2 epilogue done, hand-over observed.  NULL switches it off
+ * (the default); process-wide; the buffer must outlive the launches.
+ */
+void fswiglu_set_decode_trace(void* device_buffer);
 
 /* Human-readable name of a status code returned by this library. */
 const char* fswiglu_status_string(int status);

@@ -127,6 +127,20 @@ def norm_mlp_residual_fp32(x, gamma, w_gate, w_up, w_down, eps: float = 1e-6, re
     return out if residual is None else out + np.asarray(residual, np.float32)
 
 
+def mlp_backward_fp32(x, w_gate, w_up, w_down, dout):
+    """Gradients of out = (silu(x Wg^T) * (x Wu^T)) Wd^T with respect to x, Wg, Wu, Wd for upstream dout, written
+    out by hand in float64 (the chain rule of the expression the forward oracle implements); returned as fp32."""
+    x, w_gate, w_up, w_down, dout = (np.asarray(a, np.float64) for a in (x, w_gate, w_up, w_down, dout))
+    g, u = x @ w_gate.T, x @ w_up.T
+    s = 1.0 / (1.0 + np.exp(-g))
+    h = g * s * u
+    dh = dout @ w_down
+    dg = dh * u * s * (1.0 + g * (1.0 - s))
+    du = dh * g * s
+    grads = (dg @ w_gate + du @ w_up, dg.T @ x, du.T @ x, dout.T @ h)
+    return tuple(a.astype(np.float32) for a in grads)
+
+
 def mlp_tp_partials(x, w_gate, w_up, w_down, world_size: int, bounds) -> list[np.ndarray]:
     """fp32 partial outputs of a Megatron split over F: rank r uses rows [lo,hi) of W_gate / W_up and
     columns [lo,hi) of W_down, `bounds(F, world_size, r) -> (lo, hi)`.  Their sum is the MLP output."""
