@@ -474,6 +474,47 @@ def run_decode(name, args, dev, stream, local_rank, steps):
             "gpu_launches": int(launches), "clocks": sampler.summary()}
 
 
+def run_backward(name, args, dev, stream, local_rank, steps):
+    """Backward pass of one workload (16*M*d*F flops: seven GEMMs, two recomputing the pre-activations)."""
+    import fused_swiglu_b200 as fsw
+    from fused_swiglu_b200 import capi
+
+    cfg = WORKLOADS[name]
+    M, d, F = cfg["M"], cfg["d"], cfg["F"]
+    x, (wg, wu, wd), _ = device_inputs(name, dev)
+    dout = torch.randn((M, d), generator=torch.Generator(device=dev).manual_seed(3), device=dev).to(torch.bfloat16)
+    ws = fsw.ops.backward_workspace(M, d, F, dev)
+    grads = [torch.empty(shape, dtype=torch.bfloat16, device=dev) for shape in ((M, d), (F, d), (F, d), (d, F))]
+    sp = ctypes.c_void_p(stream.cuda_stream)
+
+    def step(record):
+        rc = capi.lib.fswiglu_mlp_backward_bf16(vp(x), d, vp(wg), vp(wu), d, vp(wd), F, vp(dout), d, vp(grads[0]), d,
+                                                vp(grads[1]), vp(grads[2]), d, vp(grads[3]), F, capi.OUT_BF16, M, d, F,
+                                                vp(ws), ws.numel(), sp)
+        capi.check(rc, "bench backward step")
+
+    for _ in range(3):
+        step(False)
+    torch.cuda.synchronize()
+    launches_before = capi.launch_count()
+    sampler = ClockSampler(local_rank)
+    total_ms = timed_region(step, steps, stream, sampler)
+    launches = capi.launch_count() - launches_before
+    assert capi.device_status(stream.cuda_stream) == 0, "device watchdog tripped (backward)"
+    ms = total_ms / steps
+    flops = 16.0 * M * d * F
+    # spot check: dW_down rows against the chain rule evaluated with torch on the device in fp32
+    h = (torch.nn.functional.silu(x.float() @ wg.float().T) * (x.float() @ wu.float().T))
+    rows = torch.tensor([0, 1, d // 2, d - 1], device=dev)
+    ref = dout.float().T[rows] @ h
+    rel = float((grads[3][rows].float() - ref).norm() / ref.norm())
+    assert rel <= 1e-2, f"backward spot check failed: {rel}"
+    return {"workload": name.replace("prefill", "backward"), "value": flops / (ms * 1e-3) / 1e12, "unit": UNIT,
+            "ms_per_step": ms, "steps": steps, "flops_per_step": flops,
+            "what": "fswiglu_mlp_backward_bf16: dx, dW_gate, dW_up, dW_down in bf16 (7 GEMMs + 6 bandwidth-bound launches)",
+            "rel_fro_dW_down_rows_vs_fp32": rel, "gpu_launches": int(launches), "clocks": sampler.summary()}
+
+
 def e2e_single(w, args):
     """The same workload through the host-buffer entry point: x from pinned host memory, result back."""
     fsw = w.fsw
@@ -617,6 +658,11 @@ def run_one_gpu(args, local_rank):
             except Exception as e:  # noqa: BLE001  (a sub-record must not take the headline down with it)
                 also.append({"workload": other, "error": f"{type(e).__name__}: {str(e)[:200]}"})
             torch.cuda.empty_cache()
+        try:
+            also.append(run_backward("c2_llama2_7b_prefill", sub, dev, stream, local_rank, steps=max(args.steps, 20)))
+        except Exception as e:  # noqa: BLE001
+            also.append({"workload": "c2_llama2_7b_backward", "error": f"{type(e).__name__}: {str(e)[:200]}"})
+        torch.cuda.empty_cache()
         line["also"] = also
     if not args.no_cpu_baseline:
         r = cpu_eager_sample(WORKLOADS[name], budget_s=20.0, steps=None, warmup=1)

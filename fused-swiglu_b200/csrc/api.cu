@@ -7,6 +7,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <chrono>
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
@@ -423,6 +424,7 @@ int launch_gemm_pair(const DeviceState& st, const void* a, int64_t lda, const vo
     const int v = std::atoi(env);
     if (v >= 1) p.group_m = std::min(v, p.num_m_tiles);
   }
+  if (const char* env = std::getenv("FSWIGLU_K_ALTERNATE")) p.k_alternate = std::atoi(env) != 0 ? 1 : 0;
   if (const char* env = std::getenv("FSWIGLU_HINT_A")) p.hint_a = std::atoi(env);
   if (const char* env = std::getenv("FSWIGLU_HINT_B")) p.hint_b = std::atoi(env);
   p.split_from = p.num_m_tiles * p.num_n_tiles;
@@ -541,14 +543,24 @@ int down_impl(DeviceState& st, const void* h, int64_t ldh, const void* w_down, i
 
 size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// Small-batch MLP: one cooperative weight-streaming launch (gate-up, hand-over, down) plus a small
-// memset of the hand-over and per-row-block arrival counters.  `h` receives the bf16 hidden
-// activations, `scratch` holds the counters and the fp32 partial tiles (decode_workspace_bytes).
+// Small-batch MLP: one cooperative weight-streaming launch (gate-up, hand-over, down), nothing else on
+// the stream.  `h` receives the bf16 hidden activations, `scratch` holds the tagged flags and the fp32
+// partial tiles (decode_workspace_bytes); nothing in it has to be initialised.
 struct Fusions {
   const float* row_scale = nullptr;  // [M] fp32, applied to gate and up before SiLU
   const void* residual = nullptr;    // bf16 [M, d], added to the output in fp32
   int64_t ld_res = 0;
 };
+
+// Per-launch tag of the small-batch kernel's flags: non-zero, never repeated within a process (2^32 launches),
+// starting from a value that differs between processes.
+uint32_t next_decode_tag() {
+  static std::atomic<uint32_t> tag{static_cast<uint32_t>(
+      std::chrono::steady_clock::now().time_since_epoch().count() * 2654435761ull >> 7)};
+  uint32_t t = tag.fetch_add(1, std::memory_order_relaxed) + 1;
+  if (t == 0) t = tag.fetch_add(1, std::memory_order_relaxed) + 1;
+  return t;
+}
 
 int decode_prefetch_units() {
   if (const char* env = std::getenv("FSWIGLU_DECODE_PREFETCH")) {
@@ -573,9 +585,7 @@ int decode_impl(DeviceState& st, const void* x, int64_t ldx, const void* w_gate,
   const int n_pad = decode_pad_tokens(M);
   const int rb2 = static_cast<int>((d + 127) / 128), kb2 = static_cast<int>((F + 63) / 64);
   uint8_t* ws = static_cast<uint8_t*>(scratch);
-  unsigned int* counters = reinterpret_cast<unsigned int*>(ws);  // [0] hand-over, then one per row-block
-  if (cudaMemsetAsync(counters, 0, static_cast<size_t>(1 + rb2) * sizeof(unsigned int), stream) != cudaSuccess)
-    return FSWIGLU_ERR_CUDA;
+  unsigned int* flags = reinterpret_cast<unsigned int*>(ws);  // per-CTA phase-1 flags, then the segment flags
 
   DecodeParams p;
   int used1 = 0;
@@ -590,8 +600,9 @@ int decode_impl(DeviceState& st, const void* x, int64_t ldx, const void* w_gate,
   p.k_blocks2 = kb2;
   p.out_f32 = out_dtype == FSWIGLU_OUT_F32 ? 1 : 0;
   p.partials = reinterpret_cast<float*>(ws + decode_counter_bytes(d));
-  p.counters = counters + 1;
-  p.handover = counters;
+  p.phase1_flags = flags;
+  p.seg_flags = flags + kDecMaxGrid + 1;
+  p.tag = next_decode_tag();
   p.M = static_cast<int>(M);
   p.n_pad = n_pad;
   p.prefetch_units = decode_prefetch_units();
@@ -616,7 +627,7 @@ int decode_impl(DeviceState& st, const void* x, int64_t ldx, const void* w_gate,
   if ((rc = encode_map(&m_down, w_down, d, F, ldw_d, 128))) return rc;
   if ((rc = encode_map(&m_h, h, M, F, F, n_pad))) return rc;
   // every CTA takes part in both phases: the grid must not exceed what phase 2 can split into
-  const int grid = std::max(1, std::min(st.num_sms, decode_grid_limit(rb2, kb2, st.num_sms)));
+  const int grid = std::max(1, std::min(std::min(st.num_sms, kDecMaxGrid), decode_grid_limit(rb2, kb2, st.num_sms)));
   if (grid < used1) decode_plan_rows(F, grid, &p.tile_rows, &p.tiles_per_cta, &used1);
   if (grid < st.num_sms) {
     if ((rc = encode_map(&m_gate, w_gate, F, d, ldw_gu, p.tile_rows))) return rc;

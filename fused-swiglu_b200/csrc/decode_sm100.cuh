@@ -22,15 +22,20 @@
 //     (128-row block, k-block) units are cut into equal contiguous ranges, one
 //     per SM (full 128-row MMAs, and each SM reads only its own k-range of h).
 //     Row-blocks whose K range spans several CTAs are combined through fp32
-//     partial tiles in a workspace; the CTA that arrives last (an atomic counter
-//     per row-block, no spinning) sums them in FIXED segment order, so results
-//     do not depend on timing;
+//     partial tiles in a workspace: every range but the first publishes its tile
+//     and raises a flag; the CTA that owns the FIRST k-range of a row-block (the
+//     last thing it does, so the others are normally done by then) adds the tiles
+//     to its own accumulator in FIXED segment order, so results do not depend on
+//     timing;
 //   * two TMA rings per SM: 11 x 16 KiB weight slots (evict-first L2 hint) and a
 //     32 KiB ring of token tiles (x in phase 1, h in phase 2).  The weight
 //     producer never waits for the hand-over: while h is being completed it
 //     already fills its ring with W_down tiles;
-//   * the only spin in the kernel is the token-tile producer waiting for the
-//     hand-over counter; it is bounded like every other wait, and the kernel is
+//   * cross-CTA signalling uses flags that carry a per-launch tag instead of counters:
+//     nothing has to be zeroed before a launch (no memset in front of the kernel), and a
+//     stale or uninitialised word never looks like a signal.  The waits on them (the
+//     token-tile producer's on the phase-1 flags of all CTAs, the reducer's on its
+//     row-block's segment flags) are bounded like every other wait, and the kernel is
 //     launched cooperatively so that all CTAs are resident together.
 #pragma once
 
@@ -68,8 +73,9 @@ struct DecodeParams {
   int k_blocks2;      // ceil(F / 64)
   int out_f32;
   float* partials;        // [row_blocks2][kDecMaxSegments][128][n_pad] fp32
-  unsigned int* counters; // [row_blocks2], zero on entry
-  unsigned int* handover; // one counter, zero on entry: CTAs that finished phase 1
+  unsigned int* seg_flags;   // [row_blocks2][kDecMaxSegments]: == tag once that segment's partial tile is published
+  unsigned int* phase1_flags;// [grid + 1]: == tag once that CTA has written its part of h
+  unsigned int tag;          // non-zero, different for every launch
   int M;                  // tokens (<= 64)
   int n_pad;              // tokens padded to 16 / 32 / 64 (the MMA N extent)
   int prefetch_units;     // how many W_down tiles ahead of the shared-memory ring are pulled into L2
@@ -107,6 +113,9 @@ __device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ void st_release_gpu(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 
 __global__ void __launch_bounds__(kDecThreads, 1)
 decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_constant__ CUtensorMap map_up,
@@ -136,7 +145,6 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
       generic_base + kDecWSlots * kDecWSlotBytes + kDecXRingBytes + 8 * (kBarsBeforeTmem + 5));
   volatile uint32_t* abort_flag = tmem_ptr_slot + 1;
   volatile uint32_t* epi_ok = tmem_ptr_slot + 2;  // two entries, alternating per tile / segment
-  volatile uint32_t* last_flag = tmem_ptr_slot + 4;
 
   const int warp = threadIdx.x >> 5;
   const uint32_t lane = lane_id();
@@ -162,7 +170,6 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
     }
     mbar_init(drain_bar, 1);
     *abort_flag = 0;
-    *last_flag = 0;
     fence_mbar_init();
     prefetch_tensormap(&map_gate);
     prefetch_tensormap(&map_up);
@@ -251,56 +258,61 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
     }
   } else if (warp == 6) {
     // ------------------- token-tile producer: x in phase 1, h (after the hand-over) in phase 2 ----
+    // Lane 0 issues the copies; the hand-over wait in the middle is done by the whole warp (every lane
+    // polls a few of the per-CTA flags).
+    const uint64_t keep = l2_policy_evict_last();
+    int slot = 0;
+    uint32_t phase = 0;
+    uint32_t issued_mask = 0, last_parity_mask = 0;
+    bool alive = true;
+    auto push = [&](const CUtensorMap* map, int kb) -> bool {
+      if (!wd.wait(x_empty(slot), phase ^ 1u, kSiteProducerEmpty)) return false;
+      mbar_arrive_expect_tx(x_full(slot), x_slot_bytes);
+      tma_load_2d_hint(x_ring + slot * x_slot_bytes, map, x_full(slot), kb * 64, 0, keep);
+      issued_mask |= 1u << slot;
+      last_parity_mask = (last_parity_mask & ~(1u << slot)) | (phase << slot);
+      if (++slot == x_slots) {
+        slot = 0;
+        phase ^= 1u;
+      }
+      return true;
+    };
     if (lane == 0) {
-      const uint64_t keep = l2_policy_evict_last();
-      int slot = 0;
-      uint32_t phase = 0;
-      uint32_t issued_mask = 0, last_parity_mask = 0;
-      bool alive = true;
-      auto push = [&](const CUtensorMap* map, int kb) -> bool {
-        if (!wd.wait(x_empty(slot), phase ^ 1u, kSiteProducerEmpty)) return false;
-        mbar_arrive_expect_tx(x_full(slot), x_slot_bytes);
-        tma_load_2d_hint(x_ring + slot * x_slot_bytes, map, x_full(slot), kb * 64, 0, keep);
-        issued_mask |= 1u << slot;
-        last_parity_mask = (last_parity_mask & ~(1u << slot)) | (phase << slot);
-        if (++slot == x_slots) {
-          slot = 0;
-          phase ^= 1u;
-        }
-        return true;
-      };
       for (int i = 0; i < p.tiles_per_cta && alive; ++i) {
         if (tile_row0(i) >= p.F) break;
         for (int kb = 0; kb < p.k_blocks1 && alive; ++kb) alive = push(&map_x, kb);
       }
-      if (alive && u_begin < u_end) {
-        // h is complete once every CTA has counted itself in (release/acquire through the counter)
-        const unsigned long long t0 = global_timer_ns();
-        while (ld_acquire_gpu(p.handover) < p.handover_target) {
-          __nanosleep(32);
-          if (wd.aborted()) {
-            alive = false;
-            break;
-          }
-          if (global_timer_ns() - t0 > p.wait_limit_ns) {
-            wd.give_up(kSiteDecode);
-            alive = false;
-            break;
-          }
+    }
+    alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;
+    if (alive && u_begin < u_end) {
+      // h is complete once every CTA has raised its phase-1 flag for this launch (release / acquire)
+      const unsigned long long t0 = global_timer_ns();
+      for (;;) {
+        bool mine = true;
+        for (unsigned int c = lane; c < p.handover_target; c += 32) mine = mine && (ld_acquire_gpu(p.phase1_flags + c) == p.tag);
+        if (__all_sync(0xffffffffu, mine)) break;
+        const bool late = global_timer_ns() - t0 > p.wait_limit_ns;
+        if (__any_sync(0xffffffffu, late || wd.aborted())) {
+          if (lane == 0 && late) wd.give_up(kSiteDecode);
+          alive = false;
+          break;
         }
-        // h was written with ordinary stores by other SMs; order them before this SM's TMA reads
-        asm volatile("fence.proxy.async;" ::: "memory");
-        stamp(kStampHandoverObserved);
+        __nanosleep(32);
       }
+      // h was written with ordinary stores by other SMs; order them before this SM's TMA reads
+      asm volatile("fence.proxy.async;" ::: "memory");
+      if (lane == 0) stamp(kStampHandoverObserved);
+    }
+    if (lane == 0) {
       for (long long u = u_begin; u < u_end && alive; ++u) {
         alive = push(&map_h, static_cast<int>(u % p.k_blocks2));
       }
       if (wd.aborted()) {
-        for (int s = 0; s < x_slots; ++s) {
-          if (issued_mask & (1u << s)) {
-            const uint32_t par = (last_parity_mask >> s) & 1u;
+        for (int sl = 0; sl < x_slots; ++sl) {
+          if (issued_mask & (1u << sl)) {
+            const uint32_t par = (last_parity_mask >> sl) & 1u;
             const unsigned long long t0 = global_timer_ns();
-            while (!mbar_try_wait(x_full(s), par)) {
+            while (!mbar_try_wait(x_full(sl), par)) {
               if (global_timer_ns() - t0 > kDrainLimitNs) {
                 wd.give_up(kSiteDrainTma);
                 break;
@@ -486,7 +498,7 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
     // fence on the critical path instead of one per thread followed by another).
     asm volatile("bar.sync 1, 128;" ::: "memory");
     if (epi_tid == 0 && alive) {
-      asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.handover) : "memory");
+      st_release_gpu(p.phase1_flags + blockIdx.x, p.tag);
       stamp(kStampP1HandoverSignalled);
     }
 
@@ -510,8 +522,7 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
       const uint32_t t_acc = tmem_base + lane_field + static_cast<uint32_t>(acc * kAccStride);
       const long long out_row = static_cast<long long>(rb) * 128 + row_in_tile;
 
-      bool reduce_here = true;
-      if (nseg > 1) {
+      if (nseg > 1 && seg != 0) {
         // publish this segment's partial sums: [row][n_pad] fp32, one contiguous run per thread
         float* my_tile =
             p.partials + ((static_cast<size_t>(rb) * kDecMaxSegments + seg) * 128 + row_in_tile) * p.n_pad;
@@ -529,60 +540,77 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
         }
         release_accumulator();  // accumulator drained: the MMA warp may reuse it
         asm volatile("bar.sync 1, 128;" ::: "memory");
+        // the barrier orders the 128 threads' stores before thread 0, whose release makes them visible
+        if (epi_tid == 0) st_release_gpu(p.seg_flags + rb * kDecMaxSegments + seg, p.tag);
+        continue;
+      }
+      if (nseg > 1) {
+        // this CTA owns the first k-range of the row-block: wait (bounded) for the other ranges' tiles
         if (epi_tid == 0) {
-          __threadfence();  // the 128 threads' partial sums (ordered before this by the barrier) become visible
-          const unsigned int old = atomicAdd(p.counters + rb, 1u);
-          *last_flag = (old == static_cast<unsigned int>(nseg - 1)) ? 1u : 0u;
-          __threadfence();
+          uint32_t ok = 1;
+          const unsigned long long t0 = global_timer_ns();
+          for (int sg = 1; sg < nseg && ok; ++sg) {
+            while (ld_acquire_gpu(p.seg_flags + rb * kDecMaxSegments + sg) != p.tag) {
+              if (wd.aborted()) {
+                ok = 0;
+                break;
+              }
+              if (global_timer_ns() - t0 > p.wait_limit_ns) {
+                wd.give_up(kSiteDecode);
+                ok = 0;
+                break;
+              }
+            }
+          }
+          epi_ok[iter & 1u] = ok;
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        reduce_here = (*last_flag != 0);
-        asm volatile("bar.sync 1, 128;" ::: "memory");  // everyone has read the flag before it is reused
+        const uint32_t ok = epi_ok[iter & 1u];
+        ++iter;
+        if (!ok) {
+          alive = false;
+          break;
+        }
       }
-      if (reduce_here) {
 #pragma unroll 1
-        for (int c0 = 0; c0 < p.n_pad; c0 += 16) {
-          float a[16];
-          if (nseg > 1) {
+      for (int c0 = 0; c0 < p.n_pad; c0 += 16) {
+        float a[16];
+        {
+          uint32_t r[16];
+          tmem_ld_32x32b_x16(t_acc + c0, r);
+          tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) a[i] = 0.0f;
-            for (int s = 0; s < nseg; ++s) {  // fixed order: the result does not depend on arrival order
-              const float* tile =
-                  p.partials + ((static_cast<size_t>(rb) * kDecMaxSegments + s) * 128 + row_in_tile) * p.n_pad;
+          for (int i = 0; i < 16; ++i) a[i] = __uint_as_float(r[i]);
+        }
+        for (int sg = 1; sg < nseg; ++sg) {  // fixed order: the result does not depend on arrival order
+          const float* tile =
+              p.partials + ((static_cast<size_t>(rb) * kDecMaxSegments + sg) * 128 + row_in_tile) * p.n_pad;
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const float4 v = __ldcg(reinterpret_cast<const float4*>(tile + c0) + i);
-                a[4 * i] += v.x; a[4 * i + 1] += v.y; a[4 * i + 2] += v.z; a[4 * i + 3] += v.w;
-              }
-            }
-          } else {
-            uint32_t r[16];
-            tmem_ld_32x32b_x16(t_acc + c0, r);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 16; ++i) a[i] = __uint_as_float(r[i]);
+          for (int i = 0; i < 4; ++i) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(tile + c0) + i);
+            a[4 * i] += v.x; a[4 * i + 1] += v.y; a[4 * i + 2] += v.z; a[4 * i + 3] += v.w;
           }
-          if (out_row < p.d) {
+        }
+        if (out_row < p.d) {
 #pragma unroll
-            for (int t = 0; t < 16; ++t) {
-              if (c0 + t < p.M) {
-                const long long off = static_cast<long long>(c0 + t) * p.ld_out + out_row;
-                float val = a[t];
-                if (p.residual != nullptr) {
-                  val += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.residual)[
-                      static_cast<long long>(c0 + t) * p.ld_res + out_row]);
-                }
-                if (p.out_f32) {
-                  reinterpret_cast<float*>(p.out)[off] = val;
-                } else {
-                  reinterpret_cast<__nv_bfloat16*>(p.out)[off] = __float2bfloat16_rn(val);
-                }
+          for (int t = 0; t < 16; ++t) {
+            if (c0 + t < p.M) {
+              const long long off = static_cast<long long>(c0 + t) * p.ld_out + out_row;
+              float val = a[t];
+              if (p.residual != nullptr) {
+                val += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.residual)[
+                    static_cast<long long>(c0 + t) * p.ld_res + out_row]);
+              }
+              if (p.out_f32) {
+                reinterpret_cast<float*>(p.out)[off] = val;
+              } else {
+                reinterpret_cast<__nv_bfloat16*>(p.out)[off] = __float2bfloat16_rn(val);
               }
             }
           }
         }
       }
-      if (nseg == 1) release_accumulator();
+      release_accumulator();
     }
     if (epi_tid == 0 && alive) stamp(kStampP2EpilogueDone);
   }
@@ -607,9 +635,10 @@ inline int decode_pad_tokens(int64_t M) { return M <= 16 ? 16 : (M <= 32 ? 32 : 
 
 inline size_t decode_round256(size_t v) { return (v + 255) / 256 * 256; }
 
-// hand-over counter + per-row-block arrival counters | phase-2 partial tiles
+// phase-1 flags (one per CTA, room for 512) + segment flags per row-block | phase-2 partial tiles
+constexpr int kDecMaxGrid = 511;
 inline size_t decode_counter_bytes(int64_t d) {
-  return decode_round256((1 + static_cast<size_t>((d + 127) / 128)) * sizeof(unsigned int));
+  return decode_round256((kDecMaxGrid + 1 + static_cast<size_t>((d + 127) / 128) * kDecMaxSegments) * sizeof(unsigned int));
 }
 inline size_t decode_workspace_bytes(int64_t M, int64_t d, int64_t) {
   const size_t n = static_cast<size_t>(decode_pad_tokens(M));

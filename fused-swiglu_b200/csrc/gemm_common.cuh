@@ -40,6 +40,8 @@ struct GemmParams {
   int num_n_tiles;
   int group_m;        // rasterisation: this many M-tiles share a sweep over N
   int hint_a, hint_b; // L2 residency class (L2Hint) of the A and B operand loads
+  int k_alternate;    // two-SM kernel: every other whole tile of a cluster walks its k-blocks backwards, so
+                      // that a wave starts on the operand columns the previous wave read last (L2 re-use)
   int vec_ok;         // 1 when every row start of `out` is 16-byte aligned
   // One-SM kernel, tail split by width: tiles with index >= split_from (the partly filled last wave
   // of the persistent schedule) are processed as two half-width units each.  split_from == number

@@ -114,8 +114,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       PairUnit un;
       bool withhold = p.withhold_one_copy != 0 && blockIdx.x == 0;  // one-shot, leader of the first pair
       const uint64_t pol_a = l2_policy_of(p.hint_a), pol_b = l2_policy_of(p.hint_b);
+      int whole_tiles = 0;
       while (alive && sched.next(&un)) {
         const TileCoord tc = tile_coord(un.tile, p);
+        const bool backwards = p.k_alternate != 0 && un.tail_tile < 0 && (whole_tiles++ & 1) != 0;
         const int m0 = tc.m_tile * 256 + static_cast<int>(rank) * 128;
         const int n0 = tc.n_tile * p.tile_n;
         const CUtensorMap* bmap = &map_b0;
@@ -128,7 +130,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         } else {
           b_row = 2 * n0 + static_cast<int>(rank) * b_half_rows;
         }
-        for (int kb = un.kb0; kb < un.kb1; ++kb) {
+        for (int step = un.kb0; step < un.kb1; ++step) {
+          const int kb = backwards ? un.kb1 - 1 - (step - un.kb0) : step;  // the sum does not care about the order
           if (!wd.wait(empty_bar(stage), phase ^ 1u, kSiteProducerEmpty)) {
             alive = false;
             break;
