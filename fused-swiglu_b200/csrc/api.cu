@@ -567,7 +567,10 @@ int decode_prefetch_units() {
     const int v = std::atoi(env);
     if (v >= 0 && v <= 4096) return v;
   }
-  return 24;  // 24 tiles x 16 KiB x 148 SMs = 57 MB ahead of the ring, well inside the L2
+  // Off by default.  Measured with per-CTA stamps at M = 16: a window of 24 tiles shortens phase 2 by
+  // 3.5 us (its loads hit the L2) but the prefetches compete with the slowest CTAs' last phase-1 loads and
+  // delay the hand-over by 5 us; a net loss until phase 1 ends more evenly.
+  return 0;
 }
 
 int decode_impl(DeviceState& st, const void* x, int64_t ldx, const void* w_gate, const void* w_up, int64_t ldw_gu,
@@ -606,9 +609,17 @@ int decode_impl(DeviceState& st, const void* x, int64_t ldx, const void* w_gate,
   p.M = static_cast<int>(M);
   p.n_pad = n_pad;
   p.prefetch_units = decode_prefetch_units();
-  // more token-tile slots for wide token tiles: 64 tokens are 8 KiB per k-block, and four of them would be
-  // only two microseconds of look-ahead
-  p.w_slots = n_pad >= 64 ? kDecWSlots - 2 : (n_pad >= 32 ? kDecWSlots - 1 : kDecWSlots);
+  // All eleven weight slots: giving two of them to the token-tile ring at M = 64 (8 instead of 4 token
+  // slots) was slower (phase 1 median 37.6 us against 36.6 us, phase 2 six microseconds longer).
+  p.w_slots = kDecWSlots;
+  // CTA c starts phase 1 at k-block 7c mod k_blocks1.  With every CTA on the same columns at the same moment
+  // the slowest CTA finished phase 1 at 42.5 us (median 36.4); staggered by 7: 37.4 us (median 34.3) - the
+  // reads then spread over the memory channels instead of marching through them in step.
+  p.k_rotate = 7;
+  if (const char* env = std::getenv("FSWIGLU_DECODE_KROT")) {  // experiments only
+    const int v = std::atoi(env);
+    if (v >= 0 && v < 4096) p.k_rotate = v;
+  }
   if (const char* env = std::getenv("FSWIGLU_DECODE_WSLOTS")) {  // experiments only
     const int v = std::atoi(env);
     if (v >= 4 && v <= kDecWSlots) p.w_slots = v;
@@ -633,6 +644,7 @@ int decode_impl(DeviceState& st, const void* x, int64_t ldx, const void* w_gate,
     if ((rc = encode_map(&m_gate, w_gate, F, d, ldw_gu, p.tile_rows))) return rc;
     if ((rc = encode_map(&m_up, w_up, F, d, ldw_gu, p.tile_rows))) return rc;
   }
+  p.rows_per_cta = p.tile_rows * p.tiles_per_cta;
   p.handover_target = static_cast<unsigned int>(grid) +
                       static_cast<unsigned int>(g_withhold_one_copy.exchange(0, std::memory_order_relaxed) != 0 ? 1 : 0);
   // Cooperative launch: the phase hand-over needs every CTA resident at the same time.

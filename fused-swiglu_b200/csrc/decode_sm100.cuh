@@ -57,6 +57,7 @@ constexpr int kDecMaxXSlots = 16;
 constexpr int kDecSmemBytes = kDecWSlots * kDecWSlotBytes + kDecXRingBytes + 1024 + 1024;
 
 constexpr int kDecMaxSegments = 8;  // partial tiles kept per row-block of phase 2
+constexpr int kDecMaxGrid = 255;    // CTAs the flag block has room for (plus one spare flag)
 
 struct DecodeParams {
   // phase 1 (row split): h[M, F] = silu(x Wg^T) * (x Wu^T)
@@ -87,6 +88,10 @@ struct DecodeParams {
   unsigned int handover_target;      // CTAs that must have finished phase 1 (= the grid size; tests of the
                                      // time-out path pass one more, which nothing ever reaches)
   int w_slots;                       // weight-tile slots in use (<= kDecWSlots); the token-tile ring takes the rest
+  int k_rotate;                      // phase 1: CTA c starts its reduction at k-block (c * k_rotate) mod k_blocks1
+                                     // and wraps around, so that the CTAs do not all read the same columns of
+                                     // the weight matrices at the same moment (0 = everybody starts at 0)
+  int rows_per_cta;                  // phase-1 hidden units per CTA (tile_rows * tiles_per_cta)
   unsigned long long* trace;         // optional: kDecTraceStamps %globaltimer stamps per CTA (profiling aid)
 };
 
@@ -191,6 +196,11 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
   auto tile_row0 = [&](int i) {
     return (static_cast<long long>(blockIdx.x) * p.tiles_per_cta + i) * p.tile_rows;
   };
+  const int kb_first = p.k_rotate > 0 ? static_cast<int>((static_cast<long long>(blockIdx.x) * p.k_rotate) % p.k_blocks1) : 0;
+  auto kb_of = [&](int step) {  // k-block handled at step `step` of a phase-1 tile
+    const int kb = kb_first + step;
+    return kb >= p.k_blocks1 ? kb - p.k_blocks1 : kb;
+  };
   // phase 2: this CTA's contiguous range of (row-block, k-block) units
   const long long units2 = static_cast<long long>(p.row_blocks2) * p.k_blocks2;
   const long long u_begin = dec_range_start(blockIdx.x, units2, gridDim.x);
@@ -220,7 +230,8 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
       for (int i = 0; i < p.tiles_per_cta && alive; ++i) {
         const long long row0 = tile_row0(i);
         if (row0 >= p.F) break;
-        for (int kb = 0; kb < p.k_blocks1 && alive; ++kb) {
+        for (int step = 0; step < p.k_blocks1 && alive; ++step) {
+          const int kb = kb_of(step);
           alive = fill(&map_gate, kb * 64, static_cast<int>(row0), tile_bytes) &&
                   fill(&map_up, kb * 64, static_cast<int>(row0), tile_bytes);
         }
@@ -280,33 +291,81 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
     if (lane == 0) {
       for (int i = 0; i < p.tiles_per_cta && alive; ++i) {
         if (tile_row0(i) >= p.F) break;
-        for (int kb = 0; kb < p.k_blocks1 && alive; ++kb) alive = push(&map_x, kb);
+        for (int step = 0; step < p.k_blocks1 && alive; ++step) alive = push(&map_x, kb_of(step));
       }
     }
     alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;
-    if (alive && u_begin < u_end) {
-      // h is complete once every CTA has raised its phase-1 flag for this launch (release / acquire)
-      const unsigned long long t0 = global_timer_ns();
-      for (;;) {
-        bool mine = true;
-        for (unsigned int c = lane; c < p.handover_target; c += 32) mine = mine && (ld_acquire_gpu(p.phase1_flags + c) == p.tag);
-        if (__all_sync(0xffffffffu, mine)) break;
+    // Phase 2 reads h.  Hidden unit j was written by CTA j / rows_per_cta, which raises its phase-1 flag for
+    // this launch when its part of h is complete; a k-block of 64 hidden units therefore depends on one or
+    // two CTAs only.  The warp keeps a bit map of the flags it has seen raised (one poll pass reads every
+    // CTA's flag, a few loads per lane, all in flight together) and lane 0 loads h tiles as far as the map
+    // allows; a new pass is made only when the next k-block's producers are not in the map yet.  So a CTA
+    // starts phase 2 as soon as ITS producers are done, not when the whole grid is.
+    constexpr int kFlagWords = (kDecMaxGrid + 32) / 32;
+    uint32_t ready[kFlagWords];
+#pragma unroll
+    for (int i = 0; i < kFlagWords; ++i) ready[i] = 0u;
+    auto is_ready = [&](unsigned int c) {
+      uint32_t word = 0u;
+#pragma unroll
+      for (int i = 0; i < kFlagWords; ++i) word = (static_cast<int>(c >> 5) == i) ? ready[i] : word;
+      return ((word >> (c & 31u)) & 1u) != 0u;
+    };
+    const unsigned int n_flags = p.handover_target;  // the grid size; one more in the time-out test
+    const bool wait_spare = n_flags > gridDim.x;      // time-out test: a flag that nothing raises
+    unsigned long long t0 = 0;
+    bool stamped = false;
+    // Running state, advanced without divisions (this loop has to keep pace with the weight stream):
+    // kb = k-block of unit u; c_hi = last CTA whose rows reach into that k-block; boundary = first hidden
+    // unit of CTA c_hi + 1; next_unseen = first CTA at or after the k-block's first producer that is not
+    // known to be done (producers of consecutive k-blocks only move upwards within a row-block).
+    int kb = static_cast<int>(u_begin % p.k_blocks2);
+    unsigned int c_hi = static_cast<unsigned int>(min(p.F - 1, kb * 64 + 63) / p.rows_per_cta);
+    long long boundary = static_cast<long long>(c_hi + 1) * p.rows_per_cta;
+    unsigned int next_unseen = static_cast<unsigned int>((kb * 64) / p.rows_per_cta);
+    long long u = u_begin;
+    while (u < u_end && alive) {
+      while (next_unseen <= c_hi && is_ready(next_unseen)) ++next_unseen;
+      if (next_unseen <= c_hi || (wait_spare && !is_ready(n_flags - 1))) {
+        // one poll pass over all flags (warp-uniform control flow: `ready` is the same in every lane)
+        if (t0 == 0) t0 = global_timer_ns();
+#pragma unroll
+        for (int i = 0; i < kFlagWords; ++i) {
+          const unsigned int c = static_cast<unsigned int>(i) * 32u + lane;
+          bool up = ((ready[i] >> lane) & 1u) != 0u;
+          if (!up && c < n_flags) up = ld_acquire_gpu(p.phase1_flags + c) == p.tag;
+          ready[i] = __ballot_sync(0xffffffffu, up);
+        }
+        // h was written with ordinary stores by other SMs; order them before this SM's TMA reads
+        asm volatile("fence.proxy.async;" ::: "memory");
         const bool late = global_timer_ns() - t0 > p.wait_limit_ns;
         if (__any_sync(0xffffffffu, late || wd.aborted())) {
           if (lane == 0 && late) wd.give_up(kSiteDecode);
           alive = false;
-          break;
         }
-        __nanosleep(32);
+        continue;
       }
-      // h was written with ordinary stores by other SMs; order them before this SM's TMA reads
-      asm volatile("fence.proxy.async;" ::: "memory");
-      if (lane == 0) stamp(kStampHandoverObserved);
+      if (lane == 0) {
+        if (!stamped) stamp(kStampHandoverObserved);
+        alive = push(&map_h, kb);
+      }
+      stamped = true;
+      alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;
+      ++u;
+      if (++kb == p.k_blocks2) {  // the range continues at the start of the next row-block
+        kb = 0;
+        c_hi = static_cast<unsigned int>(min(p.F - 1, 63) / p.rows_per_cta);
+        boundary = static_cast<long long>(c_hi + 1) * p.rows_per_cta;
+        next_unseen = 0;
+      } else {
+        const long long last_hidden = min(static_cast<long long>(p.F) - 1, static_cast<long long>(kb) * 64 + 63);
+        while (last_hidden >= boundary) {
+          ++c_hi;
+          boundary += p.rows_per_cta;
+        }
+      }
     }
     if (lane == 0) {
-      for (long long u = u_begin; u < u_end && alive; ++u) {
-        alive = push(&map_h, static_cast<int>(u % p.k_blocks2));
-      }
       if (wd.aborted()) {
         for (int sl = 0; sl < x_slots; ++sl) {
           if (issued_mask & (1u << sl)) {
@@ -635,8 +694,7 @@ inline int decode_pad_tokens(int64_t M) { return M <= 16 ? 16 : (M <= 32 ? 32 : 
 
 inline size_t decode_round256(size_t v) { return (v + 255) / 256 * 256; }
 
-// phase-1 flags (one per CTA, room for 512) + segment flags per row-block | phase-2 partial tiles
-constexpr int kDecMaxGrid = 511;
+// phase-1 flags (one per CTA, room for kDecMaxGrid + 1) + segment flags per row-block | phase-2 partial tiles
 inline size_t decode_counter_bytes(int64_t d) {
   return decode_round256((kDecMaxGrid + 1 + static_cast<size_t>((d + 127) / 128) * kDecMaxSegments) * sizeof(unsigned int));
 }
