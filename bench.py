@@ -828,7 +828,7 @@ def main():
     ap.add_argument("--tp-mode", choices=["allreduce", "rs_ag", "push"], default="push")
     ap.add_argument("--comm-sms", type=int, default=0,
                     help="SMs withheld from the GEMMs for communication kernels when N > 1 (push mode needs none)")
-    ap.add_argument("--reduce-ctas", type=int, default=64, help="CTAs of the reduce+broadcast kernel (push mode)")
+    ap.add_argument("--reduce-ctas", type=int, default=128, help="CTAs of the reduce+broadcast kernel (push mode)")
     ap.add_argument("--slab-rows", type=str, default="", help="explicit slab heights, e.g. 3840,3840,512")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gpu-baselines", action="store_true")

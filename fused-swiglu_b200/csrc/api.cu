@@ -410,6 +410,12 @@ void plan_pair_tail(GemmParams* p, int clusters, int num_kb, const Scratch& scra
   p->tail_partials = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch.ptr) + kTailCounterBytes);
 }
 
+// FSWIGLU_TAIL_HALVES=0 turns the width-split of the last wave off (experiments, A/B timing).
+bool tail_halves_enabled() {
+  const char* env = std::getenv("FSWIGLU_TAIL_HALVES");
+  return env == nullptr || env[0] != '0';
+}
+
 // `p` arrives filled for the one-SM kernel; re-plan it for 256-row pair tiles of full width.
 template <int kMode, bool kOutF32>
 int launch_gemm_pair(const DeviceState& st, const void* a, int64_t lda, const void* b0, const void* b1, int64_t ldb,
@@ -429,19 +435,32 @@ int launch_gemm_pair(const DeviceState& st, const void* a, int64_t lda, const vo
   if (const char* env = std::getenv("FSWIGLU_HINT_B")) p.hint_b = std::atoi(env);
   p.split_from = p.num_m_tiles * p.num_n_tiles;
   p.half_boxes = 0;
+  // last, partly filled wave: split along K when that clearly pays (needs scratch), else by width when its
+  // tiles fill at most half of the clusters
+  plan_pair_tail(&p, clusters, (p.K + kBlockK - 1) / kBlockK, scratch);
+  p.tail_halves = 0;
+  if (p.tail_len == 0 && tail_halves_enabled() && plan_pair_tail_halves(pairs, clusters, p.tile_n, &p.tail_first)) {
+    p.tail_halves = 1;
+  }
   int rc;
-  CUtensorMap ma, mb0, mb1;
+  CUtensorMap ma, mb0, mb1, mh0, mh1;
   if ((rc = encode_map(&ma, a, p.M, p.K, lda, 128))) return rc;
   if ((rc = encode_map(&mb0, b0, b_rows, p.K, ldb, 128))) return rc;
   mb1 = mb0;
   if (b1 != nullptr && (rc = encode_map(&mb1, b1, b_rows, p.K, ldb, 128))) return rc;
-  plan_pair_tail(&p, clusters, (p.K + kBlockK - 1) / kBlockK, scratch);
+  mh0 = mb0;
+  mh1 = mb1;
+  if (p.tail_halves) {  // the half-width units' B boxes: 64 rows
+    if ((rc = encode_map(&mh0, b0, b_rows, p.K, ldb, 64))) return rc;
+    mh1 = mh0;
+    if (b1 != nullptr && (rc = encode_map(&mh1, b1, b_rows, p.K, ldb, 64))) return rc;
+  }
   if (p.tail_len > 0 && !scratch.counters_clean) {
     if (cudaMemsetAsync(p.tail_counters, 0, kTailCounterBytes, stream) != cudaSuccess) return FSWIGLU_ERR_CUDA;
   }
   p.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
   p.withhold_one_copy = g_withhold_one_copy.exchange(0, std::memory_order_relaxed);
-  gemm_pair_kernel<kMode, kOutF32><<<2 * clusters, kGemmThreads, kPairSmemBytes, stream>>>(ma, mb0, mb1, p);
+  gemm_pair_kernel<kMode, kOutF32><<<2 * clusters, kGemmThreads, kPairSmemBytes, stream>>>(ma, mb0, mb1, mh0, mh1, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError() == cudaSuccess ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
 }
@@ -1202,7 +1221,7 @@ int fswiglu_reduce_bcast_bf16(const void* recv_local, void* const* out_ptrs, int
   }
   p.n16 = rows * cols / 8;
   p.world = world;
-  int ctas = max_ctas > 0 ? max_ctas : 64;
+  int ctas = max_ctas > 0 ? max_ctas : 128;
   const long long need = (p.n16 + 127) / 128;
   if (ctas > need) ctas = static_cast<int>(need);
   reduce_bcast_bf16_kernel<<<ctas, 128, 0, static_cast<cudaStream_t>(stream)>>>(p);

@@ -641,13 +641,31 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
 #pragma unroll
           for (int i = 0; i < 16; ++i) a[i] = __uint_as_float(r[i]);
         }
-        for (int sg = 1; sg < nseg; ++sg) {  // fixed order: the result does not depend on arrival order
-          const float* tile =
-              p.partials + ((static_cast<size_t>(rb) * kDecMaxSegments + sg) * 128 + row_in_tile) * p.n_pad;
+        if (nseg > 1) {
+          // all other segments' values for these 16 columns are requested before any is added (one round
+          // trip to L2 instead of one per segment), then summed in fixed segment order: the result does not
+          // depend on arrival order
+          float4 v[kDecMaxSegments - 1][4];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float4 v = __ldcg(reinterpret_cast<const float4*>(tile + c0) + i);
-            a[4 * i] += v.x; a[4 * i + 1] += v.y; a[4 * i + 2] += v.z; a[4 * i + 3] += v.w;
+          for (int sg = 1; sg < kDecMaxSegments; ++sg) {
+            if (sg < nseg) {
+              const float* tile =
+                  p.partials + ((static_cast<size_t>(rb) * kDecMaxSegments + sg) * 128 + row_in_tile) * p.n_pad;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) v[sg - 1][i] = __ldcg(reinterpret_cast<const float4*>(tile + c0) + i);
+            }
+          }
+#pragma unroll
+          for (int sg = 1; sg < kDecMaxSegments; ++sg) {
+            if (sg < nseg) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                a[4 * i] += v[sg - 1][i].x;
+                a[4 * i + 1] += v[sg - 1][i].y;
+                a[4 * i + 2] += v[sg - 1][i].z;
+                a[4 * i + 3] += v[sg - 1][i].w;
+              }
+            }
           }
         }
         if (out_row < p.d) {

@@ -57,6 +57,7 @@ struct GemmParams {
   // tail_len == 0 disables it (then tail_first == number of tiles).
   int tail_first;
   int tail_len;
+  int tail_halves;    // two-SM kernel: tiles from tail_first on are two half-width units each (B boxes of 64 rows)
   float* tail_partials;          // [(cluster + tail tile) * 2 + cta rank][kTailBlockFloats]
   unsigned int* tail_counters;   // [tail tile * 2 + cta rank], zero on entry, zero again on exit
   uint32_t* status;   // device watchdog word (0 = healthy)

@@ -44,7 +44,10 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
 template <int kMode, bool kOutF32>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
-                 const __grid_constant__ CUtensorMap map_b1, const GemmParams p) {
+                 const __grid_constant__ CUtensorMap map_b1, const __grid_constant__ CUtensorMap map_h0,
+                 const __grid_constant__ CUtensorMap map_h1, const GemmParams p) {
+  // map_b0 / map_b1: B operand(s) with 128-row boxes (whole tiles); map_h0 / map_h1: the same matrices with
+  // 64-row boxes, used by the half-width units of a width-split last wave only
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_base + kPairStages * kPairStageBytes;
@@ -82,6 +85,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b0);
     prefetch_tensormap(&map_b1);
+    if (p.tail_halves != 0) {
+      prefetch_tensormap(&map_h0);
+      prefetch_tensormap(&map_h1);
+    }
   }
   if (warp == 1) {
     tmem_alloc_2cta(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), kTmemCols);
@@ -100,8 +107,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int num_clusters = gridDim.x / 2;
   const int cluster_id = blockIdx.x / 2;
   const int mma_n = (kMode == kPlain) ? p.tile_n : 2 * p.tile_n;  // columns of the pair's accumulator
-  const int b_half_rows = mma_n / 2;
-  const uint32_t stage_tx_bytes = kATileBytes + static_cast<uint32_t>(b_half_rows) * (kBlockK * 2);
+  const int b_half_rows = mma_n / 2;  // B rows a CTA holds for a whole tile (128); a half-width unit takes half
 
   if (warp == 0) {
     // ------------------------------ TMA producer (both CTAs) ------------------------------
@@ -110,7 +116,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       uint32_t phase = 0;
       uint32_t issued_mask = 0, last_parity_mask = 0;
       bool alive = true;
-      PairSchedule sched(p.num_m_tiles * p.num_n_tiles, p.tail_first, p.tail_len, cluster_id, num_clusters, num_kb);
+      PairSchedule sched(p.num_m_tiles * p.num_n_tiles, p.tail_first, p.tail_len, p.tail_halves, cluster_id, num_clusters, num_kb);
       PairUnit un;
       bool withhold = p.withhold_one_copy != 0 && blockIdx.x == 0;  // one-shot, leader of the first pair
       const uint64_t pol_a = l2_policy_of(p.hint_a), pol_b = l2_policy_of(p.hint_b);
@@ -121,15 +127,21 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const int m0 = tc.m_tile * 256 + static_cast<int>(rank) * 128;
         const int n0 = tc.n_tile * p.tile_n;
         const CUtensorMap* bmap = &map_b0;
+        // B rows of this CTA: `rows` of them from b_row on (a half-width unit takes half as many, from
+        // the half's first row, through the maps with 64-row boxes)
+        const int rows = un.half < 0 ? b_half_rows : b_half_rows / 2;
+        if (un.half >= 0) bmap = &map_h0;
+        const int hsel = un.half < 0 ? 0 : un.half;
         int b_row;
         if (kMode == kPlain) {
-          b_row = n0 + static_cast<int>(rank) * b_half_rows;
+          b_row = n0 + hsel * b_half_rows + static_cast<int>(rank) * rows;
         } else if (kMode == kGatedSplit) {
-          b_row = n0;  // leader: W_gate rows, partner: W_up rows
-          if (rank == 1) bmap = &map_b1;
+          b_row = n0 + hsel * rows;  // leader: W_gate rows, partner: W_up rows
+          if (rank == 1) bmap = un.half < 0 ? &map_b1 : &map_h1;
         } else {
-          b_row = 2 * n0 + static_cast<int>(rank) * b_half_rows;
+          b_row = 2 * n0 + hsel * b_half_rows + static_cast<int>(rank) * rows;
         }
+        const uint32_t stage_tx_bytes = kATileBytes + static_cast<uint32_t>(rows) * (kBlockK * 2);
         for (int step = un.kb0; step < un.kb1; ++step) {
           const int kb = backwards ? un.kb1 - 1 - (step - un.kb0) : step;  // the sum does not care about the order
           if (!wd.wait(empty_bar(stage), phase ^ 1u, kSiteProducerEmpty)) {
@@ -140,8 +152,19 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           // one barrier per stage, in the leader: it expects the bytes of both CTAs' halves
           if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2u * stage_tx_bytes);
           const uint32_t leader_full = map_to_cta(full_bar(stage), 0);
-          tma_load_2d_pair_hint(a_dst, &map_a, leader_full, kb * kBlockK, m0, pol_a);
-          if (!withhold) tma_load_2d_pair_hint(a_dst + kATileBytes, bmap, leader_full, kb * kBlockK, b_row, pol_b);
+          // no residency class: the plain load (the hardware's default policy), else the load with a hint
+          if (p.hint_a == kL2Default) {
+            tma_load_2d_pair(a_dst, &map_a, leader_full, kb * kBlockK, m0);
+          } else {
+            tma_load_2d_pair_hint(a_dst, &map_a, leader_full, kb * kBlockK, m0, pol_a);
+          }
+          if (!withhold) {
+            if (p.hint_b == kL2Default) {
+              tma_load_2d_pair(a_dst + kATileBytes, bmap, leader_full, kb * kBlockK, b_row);
+            } else {
+              tma_load_2d_pair_hint(a_dst + kATileBytes, bmap, leader_full, kb * kBlockK, b_row, pol_b);
+            }
+          }
           withhold = false;
           issued_mask |= 1u << stage;
           last_parity_mask = (last_parity_mask & ~(1u << stage)) | (phase << stage);
@@ -176,18 +199,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   } else if (warp == 1) {
     if (lane == 0 && rank == 0) {
       // ------------------------------- leader: MMA issuer for the pair -------------------------------
-      const uint32_t idesc = umma_idesc_bf16_f32(256, mma_n);
+      const uint32_t idesc_full = umma_idesc_bf16_f32(256, mma_n);
+      const uint32_t idesc_half = umma_idesc_bf16_f32(256, mma_n / 2);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool alive = true;
-      PairSchedule sched(p.num_m_tiles * p.num_n_tiles, p.tail_first, p.tail_len, cluster_id, num_clusters, num_kb);
+      PairSchedule sched(p.num_m_tiles * p.num_n_tiles, p.tail_first, p.tail_len, p.tail_halves, cluster_id, num_clusters, num_kb);
       PairUnit un;
       while (alive && sched.next(&un)) {
         if (!wd.wait<true>(tempty_bar(acc), acc_phase ^ 1u, kSiteMmaTmemEmpty)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kUmmaN);
+        const uint32_t idesc = un.half < 0 ? idesc_full : idesc_half;
         for (int kb = un.kb0; kb < un.kb1; ++kb) {
           if (!wd.wait<true>(full_bar(stage), phase, kSiteMmaFull)) {
             alive = false;
@@ -233,7 +258,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     int acc = 0;
     uint32_t acc_phase = 0;
     uint32_t iter = 0;
-    PairSchedule sched(p.num_m_tiles * p.num_n_tiles, p.tail_first, p.tail_len, cluster_id, num_clusters, num_kb);
+    PairSchedule sched(p.num_m_tiles * p.num_n_tiles, p.tail_first, p.tail_len, p.tail_halves, cluster_id, num_clusters, num_kb);
     PairUnit un;
     while (sched.next(&un)) {
       const TileCoord tc = tile_coord(un.tile, p);
@@ -247,7 +272,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       tc_fence_after_sync();
       const uint32_t t_acc = tmem_base + lane_field + static_cast<uint32_t>(acc * kUmmaN);
       const int row0 = tc.m_tile * 256 + static_cast<int>(rank) * 128 + quarter * 32;
-      const int col_base = tc.n_tile * p.tile_n;
+      const int width = un.half < 0 ? p.tile_n : p.tile_n / 2;
+      const int col_base = tc.n_tile * p.tile_n + (un.half > 0 ? width : 0);
       auto release_accumulator = [&]() {
         // this warp is done with the accumulator: tell the leader's MMA issuer (one arrival per warp)
         tc_fence_before_sync();
@@ -267,7 +293,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       int nseg = 1, seg = 0;
       if (un.tail_tile >= 0) tail_tile_segments(un.tail_tile, num_kb, p.tail_len, cluster_id, &nseg, &seg);
       if (nseg == 1) {
-        epilogue_rows<kMode, kOutF32>(p, TmemSource{t_acc}, warp_stage, lane, row0, col_base, p.tile_n);
+        epilogue_rows<kMode, kOutF32>(p, TmemSource{t_acc}, warp_stage, lane, row0, col_base, width);
         release_accumulator();
         continue;
       }

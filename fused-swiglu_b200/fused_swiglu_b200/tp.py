@@ -123,7 +123,7 @@ class TensorParallelSwiGLU:
     def __init__(self, w_gate_shard: torch.Tensor, w_up_shard: torch.Tensor, w_down_shard: torch.Tensor,
                  group: Optional[dist.ProcessGroup] = None, n_slabs: int = 0, mode: str = "push",
                  local_partial: Callable = _cuda_local_partial, round_fn: Callable = _cuda_round,
-                 comm_sms: int = 16, wire_dtype: torch.dtype = torch.float32, reduce_ctas: int = 0,
+                 comm_sms: int = 0, wire_dtype: torch.dtype = torch.float32, reduce_ctas: int = 0,
                  slab_rows: Optional[list] = None):
         if mode not in ("allreduce", "rs_ag", "push"):
             raise ValueError("mode must be 'allreduce', 'rs_ag' or 'push'")
@@ -146,7 +146,10 @@ class TensorParallelSwiGLU:
         self._bufs = {}
         self._cuda = self.device.type == "cuda"
         self._comm_stream = torch.cuda.Stream(device=self.device, priority=-1) if self._cuda else None
-        self._reduce_ctas = reduce_ctas if reduce_ctas > 0 else max(8, comm_sms)
+        # reduce + broadcast kernel (push mode): 128 CTAs of 128 threads, one beside each GEMM CTA on most SMs.
+        # Measured on 8 GPUs at the 70B shape: 64 CTAs 1.360 ms per step (the reduction of the first slab
+        # outlasts the second slab's GEMMs), 128 CTAs 1.264 ms.
+        self._reduce_ctas = reduce_ctas if reduce_ctas > 0 else 128
         self._xin = None
         # explicit slab heights (rows), e.g. [3840, 3840, 512]; every slab but the last must be a
         # multiple of 8 * world.  None: n_slabs equal slabs.
@@ -155,6 +158,8 @@ class TensorParallelSwiGLU:
         # stream), "barrier_end", "reduce_end" (communication stream) of every slab and at "final_barrier_end" (slab
         # -1); a benchmark records an event on `stream` there to time the phases
         self.trace = None
+        if mode != "push" and comm_sms == 0:
+            comm_sms = 16  # NCCL kernels cannot share an SM with a persistent GEMM CTA
         if self._cuda and self.world > 1 and comm_sms > 0:
             # leave `comm_sms` SMs to the collective kernels that run beside the GEMMs (the launcher
             # should cap NCCL to the same number, e.g. NCCL_MAX_CTAS), see fswiglu_set_max_ctas

@@ -35,7 +35,7 @@ int main() {
           std::map<int, std::vector<std::pair<int, int>>> segs;  // tail tile -> (cluster, kb0) in cluster order
           std::set<int> blocks;
           for (int c = 0; c < clusters; ++c) {
-            PairSchedule s(tiles, tail_first, tail_len, c, clusters, num_kb);
+            PairSchedule s(tiles, tail_first, tail_len, 0, c, clusters, num_kb);
             PairUnit u;
             int guard = 0;
             while (s.next(&u)) {
@@ -78,8 +78,35 @@ int main() {
       }
     }
   }
+  // width-split of the last wave: every column half of every tail tile exactly once, whole tiles untouched
+  for (int clusters : cluster_values) {
+    for (int tiles = 1; tiles <= 4 * clusters + 3; ++tiles) {
+      int tail_first = tiles;
+      const bool on = plan_pair_tail_halves(tiles, clusters, 128, &tail_first);
+      if (!on) continue;
+      if (tail_first % clusters != 0 || 2 * (tiles - tail_first) > clusters) return fail("halves plan", tiles, clusters, 0, 3);
+      std::vector<int> whole(tiles, 0), left(tiles, 0), right(tiles, 0);
+      for (int c = 0; c < clusters; ++c) {
+        PairSchedule s(tiles, tail_first, 0, 1, c, clusters, 5);
+        PairUnit u;
+        int guard = 0;
+        while (s.next(&u)) {
+          if (++guard > tiles + 4) return fail("halves schedule does not terminate", tiles, clusters, 5, 3);
+          if (u.kb0 != 0 || u.kb1 != 5 || u.tail_tile != -1) return fail("half unit with a k range", tiles, clusters, 5, 3);
+          if (u.half < 0) whole[u.tile]++; else if (u.half == 0) left[u.tile]++; else right[u.tile]++;
+          if (u.half >= 0 && u.tile < tail_first) return fail("half unit outside the tail", tiles, clusters, 5, 3);
+        }
+      }
+      for (int t = 0; t < tiles; ++t) {
+        const bool tail = t >= tail_first;
+        if (whole[t] != (tail ? 0 : 1) || left[t] != (tail ? 1 : 0) || right[t] != (tail ? 1 : 0))
+          return fail("halves coverage", tiles, clusters, 5, 3);
+      }
+      ++cases;
+    }
+  }
   // the shapes the benchmark configurations produce on 74 clusters
-  struct { int tiles, kb; bool split; } known[] = {{256, 172, true}, {1376, 64, true}, {1024, 448, true}, {7168, 128, false}};
+  struct { int tiles, kb; bool split; } known[] = {{256, 172, false}, {1376, 64, false}, {1024, 448, false}, {4, 2048, true}};
   for (auto& k : known) {
     int tf = 0, tl = 0;
     plan_pair_tail_split(k.tiles, 74, k.kb, 1, &tf, &tl);

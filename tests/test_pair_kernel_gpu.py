@@ -217,10 +217,41 @@ def test_split_last_wave_matches_unsplit(fsw, cuda_dev, M, d, F, ctas):
     assert m["rel_fro"] <= 1e-5, m
 
 
+@pytest.mark.parametrize("M,d,F,ctas_gu,ctas_dn", [(300, 1024, 264, 10, 14), (513, 2048, 520, 28, 46),
+                                                   (1500, 1536, 1096, 100, 60), (4096, 5120, 1408, 0, 0)])
+def test_width_split_last_wave_is_bit_identical(fsw, cuda_dev, M, d, F, ctas_gu, ctas_dn):
+    """When the last wave's tiles fill at most half of the clusters they are processed as two half-width
+    units each (64-row operand boxes, N = 128 MMAs).  Same k order as a whole tile, so every mode and output
+    type must equal the unsplit two-SM kernel and the one-SM kernel bit for bit.  The SM budgets make the
+    tile counts leave such a remainder: gate-up 6 tiles on 5 clusters, 15 on 14, 54 on 50, 176 on 74; down
+    8 on 7, 24 on 23, 36 on 30, 320 on 74."""
+    x, wg, wu, wd = fsw.inputs.make_mlp_inputs(M, d, F, seed=M + 1)
+    wg, wu = wg * 25, wu * 25
+    xd, gd, ud, dd = (t.to(cuda_dev) for t in (x, wg, wu, wd))
+    w13 = fsw.pack.interleave_up_gate(ud, gd)
+    res = {}
+    for name, envs in (("halves", dict(FSWIGLU_PAIR="force", FSWIGLU_TAIL_SPLITK="0")),
+                       ("whole", dict(FSWIGLU_PAIR="force", FSWIGLU_TAIL_SPLITK="0", FSWIGLU_TAIL_HALVES="0")),
+                       ("one_sm", dict(FSWIGLU_PAIR="0"))):
+        with env(**envs), sm_budget(fsw, ctas_gu):
+            h = fsw.ops.fused_swiglu_gateup_bf16(xd, gd, ud)
+            hp = fsw.ops.fused_swiglu_bf16(xd, w13)
+        with env(**envs), sm_budget(fsw, ctas_dn):
+            o = fsw.ops.swiglu_down_bf16(h, dd)
+            of = fsw.ops.swiglu_down_bf16(h, dd, out_dtype=torch.float32)
+        healthy(fsw)
+        res[name] = (h, hp, o, of)
+    for other in ("whole", "one_sm"):
+        for a, b in zip(res["halves"], res[other]):
+            assert torch.equal(a, b), other
+    m = orc.error_metrics(f32(res["halves"][0]), orc.gateup_split_fp32acc(f32(x), f32(wg), f32(wu)))
+    assert m["rel_fro"] <= 1e-3 and m["scaled_max_abs"] <= 2.0 ** -7, m
+
+
 def test_split_last_wave_is_used_at_the_7b_shape_and_matches(fsw, cuda_dev):
-    """Down projection at the 7B prefill shape (256 pair tiles on 74 clusters = 3.46 waves): the split is
-    chosen without any override; rows are compared with the CPU oracle and the whole output with the
-    unsplit kernel."""
+    """Down projection at the 7B prefill shape (256 pair tiles on 74 clusters = 3.46 waves) with the split along
+    K forced (by default this shape takes the width split, which is bit-identical to the unsplit kernel);
+    rows are compared with the CPU oracle and the whole output with the unsplit kernel."""
     M, d, F = 4096, 4096, 11008
     g = torch.Generator().manual_seed(5)
     h = torch.randn((M, F), generator=g).to(torch.bfloat16)
@@ -229,8 +260,9 @@ def test_split_last_wave_is_used_at_the_7b_shape_and_matches(fsw, cuda_dev):
     scratch = fsw.ops.gemm_scratch(cuda_dev)
     with env(FSWIGLU_TAIL_SPLITK="0"):
         o0 = fsw.ops.swiglu_down_bf16(hd, wdd, scratch=scratch)
-    o1 = fsw.ops.swiglu_down_bf16(hd, wdd, scratch=scratch)
-    o2 = fsw.ops.swiglu_down_bf16(hd, wdd, scratch=scratch)
+    with env(FSWIGLU_TAIL_SPLITK="force"):
+        o1 = fsw.ops.swiglu_down_bf16(hd, wdd, scratch=scratch)
+        o2 = fsw.ops.swiglu_down_bf16(hd, wdd, scratch=scratch)
     healthy(fsw)
     assert torch.equal(o1, o2)
     assert not torch.equal(o0, o1), "the split was expected to change the summation order of the last wave"
