@@ -70,7 +70,7 @@ FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_g
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from `ncu` captures of one
 # launch at the full workload size (profiles/): two-SM gate-up GEMM at the 7B prefill shape; small-batch
 # kernel at M = 16 (the other small-batch sizes stream the same weights).
-NCU_TRAFFIC_BYTES = {"c2_llama2_7b_prefill": 238.52e6 + 82.92e6, "c3_llama3_8b_decode_m16": 353.64e6 + 3.78e6}
+NCU_TRAFFIC_BYTES = {"c2_llama2_7b_prefill": 260.40e6 + 84.79e6, "c3_llama3_8b_decode_m16": 357.20e6 + 4.04e6}
 PARITY_REL_FRO = 5e-3
 PARITY_SCALED_MAX_ABS = 8e-3
 
