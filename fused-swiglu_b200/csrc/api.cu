@@ -18,6 +18,7 @@
 #include "decode_sm100.cuh"
 #include "elementwise_sm100.cuh"
 #include "gemm_pair_sm100.cuh"
+#include "gemm_quad_sm100.cuh"
 #include "gemm_sm100.cuh"
 
 namespace fsw {
@@ -187,6 +188,10 @@ int prepare_device(int dev, int* num_sms) {
   e = e ? e : opt_in_smem(gemm_pair_kernel<kPlain, true>, kPairSmemBytes);
   e = e ? e : opt_in_smem(gemm_pair_kernel<kGatedSplit, false>, kPairSmemBytes);
   e = e ? e : opt_in_smem(gemm_pair_kernel<kGatedInterleaved, false>, kPairSmemBytes);
+  e = e ? e : opt_in_smem(gemm_quad_kernel<kPlain, false>, kQuadSmemBytes);
+  e = e ? e : opt_in_smem(gemm_quad_kernel<kPlain, true>, kQuadSmemBytes);
+  e = e ? e : opt_in_smem(gemm_quad_kernel<kGatedSplit, false>, kQuadSmemBytes);
+  e = e ? e : opt_in_smem(gemm_quad_kernel<kGatedInterleaved, false>, kQuadSmemBytes);
   return e == cudaSuccess ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
 }
 
@@ -465,6 +470,85 @@ int launch_gemm_pair(const DeviceState& st, const void* a, int64_t lda, const vo
   return cudaGetLastError() == cudaSuccess ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
 }
 
+// 512-row tiles (gemm_quad_sm100.cuh).  They move 0.75 x the operand bytes per flop through the SMs and fewer
+// through HBM, which under the power cap buys clock; but there is no second accumulator stage, and a wave is 74
+// tiles of 512 x 256 outputs, so a partly filled last wave costs more.  Measured on B200 in 0.6 s loops
+// (same process, results bit-identical): down projection at the 70B shape 2.85 ms against 2.98-3.09 ms
+// (1352 against 1245-1291 TF/s), at the 7B shape 0.305 against 0.317 ms; gate-up at the 70B shape 5.90-5.98
+// against 5.87 ms and at the 7B shape 0.60 against 0.52-0.55 ms - the gated epilogue's exposed half and the
+// coarser wave eat the gain.  So: plain mode only, and only when the schedule's own arithmetic favours it with
+// a per-tile advantage of 6 % (the smaller of the two measured).  FSWIGLU_QUAD=0 never, =force always (tests).
+constexpr double kQuadTileAdvantage = 0.06;
+int quad_mode() {  // 0 never, 1 automatic, 2 always
+  const char* env = std::getenv("FSWIGLU_QUAD");
+  if (env == nullptr || env[0] == '\0') return 1;
+  if (env[0] == '0') return 0;
+  return (env[0] == 'f' || env[0] == 'F') ? 2 : 1;
+}
+bool use_quad_kernel(const DeviceState& st, const GemmParams& p, int tile_n, bool gated) {
+  const int mode = quad_mode();
+  if (mode == 0 || effective_ctas(st) < 2 || pair_mode() == 0) return false;
+  if (mode == 2) return true;
+  if (gated) return false;
+  if (pair_mode() == 2) return false;     // the 256-row kernel was asked for by name
+  if (p.scatter_world > 0) return false;  // row slabs of a tensor-parallel step: few waves each
+  const int64_t clusters = effective_ctas(st) / 2;
+  const int64_t n_tiles = (p.n_out + tile_n - 1) / tile_n;
+  const int64_t quad = ((p.M + 511) / 512) * n_tiles, pair = ((p.M + 255) / 256) * n_tiles;
+  if (pair < clusters) return false;  // below one wave the one-SM kernel takes over
+  // cost in units of one 256-row tile's main loop
+  const double quad_cost = 2.0 * static_cast<double>((quad + clusters - 1) / clusters) * (1.0 - kQuadTileAdvantage);
+  const int64_t rem = pair % clusters;
+  // the 256-row kernel's last wave: half-width units (about 0.6 of a tile's time) when it is at most half full
+  const double pair_cost = static_cast<double>(pair / clusters) + (rem == 0 ? 0.0 : (2 * rem <= clusters ? 0.6 : 1.0));
+  return quad_cost < pair_cost;
+}
+
+// Raster for 512-row tiles: the same reasoning as pick_pair_group_m with twice the rows per M-tile.
+int pick_quad_group_m(int num_m_tiles, int num_n_tiles, int64_t K, int clusters) {
+  const int64_t a_bytes = 512 * K * 2, b_bytes = 256 * K * 2;
+  const int64_t resident = 48ll << 20;
+  int g;
+  if (num_n_tiles * b_bytes <= resident) {
+    g = (clusters + num_n_tiles - 1) / num_n_tiles;
+  } else if (num_m_tiles * a_bytes <= resident) {
+    g = num_m_tiles;
+  } else {
+    // measured at the 70B shape (gate-up / down TF/s in 0.6 s loops): g = 2 1248 / 1275, 4 1294 / 1358,
+    // 8 1318 / 1359, 16 1283 / 1319
+    g = 1;
+    while ((g + 1) * (g + 1) <= clusters) ++g;  // floor(sqrt(clusters)): 8 for 74 clusters
+  }
+  return std::max(1, std::min(g, num_m_tiles));
+}
+
+// `p` arrives filled for the one-SM kernel; re-plan it for 512-row tiles of full width.
+template <int kMode, bool kOutF32>
+int launch_gemm_quad(const DeviceState& st, const void* a, int64_t lda, const void* b0, const void* b1, int64_t ldb,
+                     int64_t b_rows, GemmParams p, cudaStream_t stream) {
+  p.tile_n = (kMode == kPlain) ? 256 : 128;
+  p.num_m_tiles = (p.M + 511) / 512;
+  p.num_n_tiles = (p.n_out + p.tile_n - 1) / p.tile_n;
+  const int tiles = p.num_m_tiles * p.num_n_tiles;
+  const int clusters = std::max(1, std::min(tiles, effective_ctas(st) / 2));
+  p.group_m = pick_quad_group_m(p.num_m_tiles, p.num_n_tiles, p.K, clusters);
+  if (const char* env = std::getenv("FSWIGLU_GROUP_M")) {  // experiments only
+    const int v = std::atoi(env);
+    if (v >= 1) p.group_m = std::min(v, p.num_m_tiles);
+  }
+  int rc;
+  CUtensorMap ma, mb0, mb1;
+  if ((rc = encode_map(&ma, a, p.M, p.K, lda, 128))) return rc;
+  if ((rc = encode_map(&mb0, b0, b_rows, p.K, ldb, 128))) return rc;
+  mb1 = mb0;
+  if (b1 != nullptr && (rc = encode_map(&mb1, b1, b_rows, p.K, ldb, 128))) return rc;
+  p.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
+  p.withhold_one_copy = g_withhold_one_copy.exchange(0, std::memory_order_relaxed);
+  gemm_quad_kernel<kMode, kOutF32><<<2 * clusters, kQuadThreads, kQuadSmemBytes, stream>>>(ma, mb0, mb1, p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
+}
+
 int gateup_impl(DeviceState& st, const void* x, int64_t ldx, const void* w0, int64_t ldw,
                 const void* w_up, void* h, int64_t ldh, int64_t M, int64_t F, int64_t d,
                 int interleaved, const float* row_scale, const Scratch& scratch, cudaStream_t stream) {
@@ -490,6 +574,10 @@ int gateup_impl(DeviceState& st, const void* x, int64_t ldx, const void* w0, int
   p.vec_ok = (aligned16(h) && ldh % 8 == 0) ? 1 : 0;
   p.status = st.status;
   p.row_scale = row_scale;
+  if (use_quad_kernel(st, p, 128, true)) {
+    return interleaved ? launch_gemm_quad<kGatedInterleaved, false>(st, x, ldx, w0, nullptr, ldw, 2 * F, p, stream)
+                       : launch_gemm_quad<kGatedSplit, false>(st, x, ldx, w0, w_up, ldw, F, p, stream);
+  }
   if (use_pair_kernel(st, M, F, 128)) {
     return interleaved
                ? launch_gemm_pair<kGatedInterleaved, false>(st, x, ldx, w0, nullptr, ldw, 2 * F, p, scratch, stream)
@@ -544,6 +632,10 @@ int down_impl(DeviceState& st, const void* h, int64_t ldh, const void* w_down, i
   p.status = st.status;
   p.residual = residual;
   p.ld_res = ldr;
+  if (use_quad_kernel(st, p, 256, false)) {
+    return f32 ? launch_gemm_quad<kPlain, true>(st, h, ldh, w_down, nullptr, ldw, d, p, stream)
+               : launch_gemm_quad<kPlain, false>(st, h, ldh, w_down, nullptr, ldw, d, p, stream);
+  }
   if (use_pair_kernel(st, M, d, 256)) {
     return f32 ? launch_gemm_pair<kPlain, true>(st, h, ldh, w_down, nullptr, ldw, d, p, scratch, stream)
                : launch_gemm_pair<kPlain, false>(st, h, ldh, w_down, nullptr, ldw, d, p, scratch, stream);
@@ -638,6 +730,12 @@ int decode_impl(DeviceState& st, const void* x, int64_t ldx, const void* w_gate,
   if (const char* env = std::getenv("FSWIGLU_DECODE_KROT")) {  // experiments only
     const int v = std::atoi(env);
     if (v >= 0 && v < 4096) p.k_rotate = v;
+  }
+  // Row-block owners sum the other k-ranges' partial tiles from shared memory (bulk copies into the idle
+  // rings).  Measured at the 8B shape: M = 64 94.9 -> 87.3 us, M <= 16 78.8 -> 78.1 us.
+  p.reduce_via_smem = 1;
+  if (const char* env = std::getenv("FSWIGLU_DECODE_SMEMRED")) {  // experiments and tests: 0 = sum from the workspace
+    if (std::atoi(env) == 0) p.reduce_via_smem = 0;
   }
   if (const char* env = std::getenv("FSWIGLU_DECODE_WSLOTS")) {  // experiments only
     const int v = std::atoi(env);

@@ -26,7 +26,9 @@
 //     and raises a flag; the CTA that owns the FIRST k-range of a row-block (the
 //     last thing it does, so the others are normally done by then) adds the tiles
 //     to its own accumulator in FIXED segment order, so results do not depend on
-//     timing;
+//     timing.  By then the CTA's shared-memory rings are idle, so the tiles are pulled
+//     into shared memory by bulk copies (one round trip for all of them instead of one
+//     per 16 token columns);
 //   * two TMA rings per SM: 11 x 16 KiB weight slots (evict-first L2 hint) and a
 //     32 KiB ring of token tiles (x in phase 1, h in phase 2).  The weight
 //     producer never waits for the hand-over: while h is being completed it
@@ -92,6 +94,8 @@ struct DecodeParams {
                                      // and wraps around, so that the CTAs do not all read the same columns of
                                      // the weight matrices at the same moment (0 = everybody starts at 0)
   int rows_per_cta;                  // phase-1 hidden units per CTA (tile_rows * tiles_per_cta)
+  int reduce_via_smem;               // phase 2: the row-block owner copies the other ranges' partial tiles into
+                                     // its (by then idle) shared-memory rings with bulk copies and sums from there
   unsigned long long* trace;         // optional: kDecTraceStamps %globaltimer stamps per CTA (profiling aid)
 };
 
@@ -122,6 +126,28 @@ __device__ __forceinline__ void st_release_gpu(unsigned int* p, unsigned int v) 
   asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+__device__ __forceinline__ unsigned int ld_relaxed_gpu(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Global -> shared bulk copy (no tensor map; both addresses 16-byte aligned, size a multiple of 16),
+// completion counted in bytes on an mbarrier of this CTA.
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+// Position (in 16-byte units) of the q-th group of four token columns inside a weight row's run of a partial
+// tile.  Thread = row; rows are n_pad * 4 bytes apart, so without a permutation the eight lanes of a
+// shared-memory access phase would all hit the same banks.  XOR with the row number (taken per 128 bytes)
+// spreads them; writer and reader use the same function.
+__device__ __forceinline__ int partial_pos(int q, int row, int groups_per_row) {
+  const int s = groups_per_row >= 8 ? row : (row >> 1);
+  return q ^ (s & (groups_per_row - 1));
+}
+
 __global__ void __launch_bounds__(kDecThreads, 1)
 decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_constant__ CUtensorMap map_up,
                     const __grid_constant__ CUtensorMap map_down, const __grid_constant__ CUtensorMap map_x,
@@ -145,6 +171,7 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
   auto tfull_bar = [&](int a) { return bar_base + 8u * (kBarsBeforeTmem + a); };
   auto tempty_bar = [&](int a) { return bar_base + 8u * (kBarsBeforeTmem + 2 + a); };
   const uint32_t drain_bar = bar_base + 8u * (kBarsBeforeTmem + 4);
+  const uint32_t reduce_bar = bar_base + 8u * (kBarsBeforeTmem + 7);  // after the four words behind the TMEM pointer
   uint8_t* generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
   volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(
       generic_base + kDecWSlots * kDecWSlotBytes + kDecXRingBytes + 8 * (kBarsBeforeTmem + 5));
@@ -174,6 +201,7 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
       mbar_init(tempty_bar(a), 128);
     }
     mbar_init(drain_bar, 1);
+    mbar_init(reduce_bar, 1);
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tensormap(&map_gate);
@@ -504,6 +532,10 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
     uint32_t acc_phase = 0;
     bool alive = true;
     uint32_t iter = 0;
+    uint32_t reduce_phase = 0;
+    const int groups_per_row = p.n_pad >> 2;               // 16-byte groups of a weight row's run in a partial tile
+    const int tile_bytes = 128 * p.n_pad * 4;              // one partial tile
+    constexpr int ring_bytes = kDecWSlots * kDecWSlotBytes + kDecXRingBytes;
     // One thread waits for the accumulator and tells the other 127: the four epilogue warps share
     // named barriers below, so they must all take the same exit if a wait gives up.
     auto accumulator_ready = [&]() -> bool {
@@ -592,7 +624,7 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            __stcg(reinterpret_cast<float4*>(my_tile + c0) + i,
+            __stcg(reinterpret_cast<float4*>(my_tile) + partial_pos((c0 >> 2) + i, row_in_tile, groups_per_row),
                    make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
                                __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3])));
           }
@@ -603,21 +635,56 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
         if (epi_tid == 0) st_release_gpu(p.seg_flags + rb * kDecMaxSegments + seg, p.tag);
         continue;
       }
+      int n_smem = 0;  // how many of the other ranges' tiles are summed from shared memory
       if (nseg > 1) {
-        // this CTA owns the first k-range of the row-block: wait (bounded) for the other ranges' tiles
+        // This CTA owns the first k-range of the row-block, and the row-block continues in other CTAs, so this
+        // is the last thing the CTA does: its shared-memory rings are idle (every copy into them was consumed
+        // by MMAs that have completed, or this accumulator would not be ready).
+        if (p.reduce_via_smem) n_smem = min(nseg - 1, ring_bytes / tile_bytes);
         if (epi_tid == 0) {
+          // wait (bounded) for the other ranges' flags: all polled together, one round trip per pass
           uint32_t ok = 1;
+          uint32_t pending = (1u << nseg) - 2u;  // bits 1 .. nseg-1
+          const unsigned int* flags = p.seg_flags + rb * kDecMaxSegments;
           const unsigned long long t0 = global_timer_ns();
-          for (int sg = 1; sg < nseg && ok; ++sg) {
-            while (ld_acquire_gpu(p.seg_flags + rb * kDecMaxSegments + sg) != p.tag) {
-              if (wd.aborted()) {
-                ok = 0;
-                break;
-              }
-              if (global_timer_ns() - t0 > p.wait_limit_ns) {
-                wd.give_up(kSiteDecode);
-                ok = 0;
-                break;
+          while (true) {
+            unsigned int seen[kDecMaxSegments];
+#pragma unroll
+            for (int sg = 1; sg < kDecMaxSegments; ++sg) seen[sg] = ((pending >> sg) & 1u) ? ld_relaxed_gpu(flags + sg) : p.tag;
+#pragma unroll
+            for (int sg = 1; sg < kDecMaxSegments; ++sg) {
+              if (seen[sg] == p.tag) pending &= ~(1u << sg);
+            }
+            if (pending == 0u) break;
+            if (wd.aborted()) {
+              ok = 0;
+              break;
+            }
+            if (global_timer_ns() - t0 > p.wait_limit_ns) {
+              wd.give_up(kSiteDecode);
+              ok = 0;
+              break;
+            }
+          }
+          asm volatile("fence.acq_rel.gpu;" ::: "memory");  // the relaxed polls above become an acquire
+          if (ok && n_smem > 0) {
+            // the tiles were written with ordinary stores by other SMs; order them before the bulk copies' reads
+            asm volatile("fence.proxy.async;" ::: "memory");
+            mbar_arrive_expect_tx(reduce_bar, static_cast<uint32_t>(n_smem * tile_bytes));
+            for (int sg = 1; sg <= n_smem; ++sg) {
+              bulk_copy_g2s(smem_base + static_cast<uint32_t>((sg - 1) * tile_bytes),
+                            p.partials + (static_cast<size_t>(rb) * kDecMaxSegments + sg) * 128 * p.n_pad,
+                            static_cast<uint32_t>(tile_bytes), reduce_bar);
+            }
+            if (!wd.wait(reduce_bar, reduce_phase, kSiteDecode)) {
+              ok = 0;
+              // the copies are under way and will land: give them time before the CTA lets go of its memory
+              const unsigned long long t1 = global_timer_ns();
+              while (!mbar_try_wait(reduce_bar, reduce_phase)) {
+                if (global_timer_ns() - t1 > kDrainLimitNs) {
+                  wd.give_up(kSiteDrainTma);
+                  break;
+                }
               }
             }
           }
@@ -629,6 +696,12 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
         if (!ok) {
           alive = false;
           break;
+        }
+        if (n_smem > 0) {
+          // thread 0 has seen the copies complete; every reader takes its own acquire on the barrier (the
+          // phase is over, so this returns at once)
+          (void)mbar_try_wait(reduce_bar, reduce_phase);
+          reduce_phase ^= 1u;
         }
       }
 #pragma unroll 1
@@ -642,28 +715,48 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_c
           for (int i = 0; i < 16; ++i) a[i] = __uint_as_float(r[i]);
         }
         if (nseg > 1) {
-          // all other segments' values for these 16 columns are requested before any is added (one round
-          // trip to L2 instead of one per segment), then summed in fixed segment order: the result does not
-          // depend on arrival order
-          float4 v[kDecMaxSegments - 1][4];
+          // Summed in fixed segment order: the result does not depend on arrival order.  Tiles in shared
+          // memory first (they are segments 1 .. n_smem); what did not fit is read from the workspace, all
+          // requests for these 16 columns in flight before any value is added.
+          int pos[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) pos[i] = partial_pos((c0 >> 2) + i, row_in_tile, groups_per_row);
 #pragma unroll
           for (int sg = 1; sg < kDecMaxSegments; ++sg) {
-            if (sg < nseg) {
-              const float* tile =
-                  p.partials + ((static_cast<size_t>(rb) * kDecMaxSegments + sg) * 128 + row_in_tile) * p.n_pad;
-#pragma unroll
-              for (int i = 0; i < 4; ++i) v[sg - 1][i] = __ldcg(reinterpret_cast<const float4*>(tile + c0) + i);
-            }
-          }
-#pragma unroll
-          for (int sg = 1; sg < kDecMaxSegments; ++sg) {
-            if (sg < nseg) {
+            if (sg <= n_smem) {
+              const float4* row = reinterpret_cast<const float4*>(
+                  generic_base + static_cast<size_t>(sg - 1) * tile_bytes + static_cast<size_t>(row_in_tile) * p.n_pad * 4);
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
-                a[4 * i] += v[sg - 1][i].x;
-                a[4 * i + 1] += v[sg - 1][i].y;
-                a[4 * i + 2] += v[sg - 1][i].z;
-                a[4 * i + 3] += v[sg - 1][i].w;
+                const float4 w = row[pos[i]];
+                a[4 * i] += w.x;
+                a[4 * i + 1] += w.y;
+                a[4 * i + 2] += w.z;
+                a[4 * i + 3] += w.w;
+              }
+            }
+          }
+          if (n_smem < nseg - 1) {
+            float4 v[kDecMaxSegments - 1][4];
+#pragma unroll
+            for (int sg = 1; sg < kDecMaxSegments; ++sg) {
+              if (sg > n_smem && sg < nseg) {
+                const float4* row = reinterpret_cast<const float4*>(
+                    p.partials + ((static_cast<size_t>(rb) * kDecMaxSegments + sg) * 128 + row_in_tile) * p.n_pad);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) v[sg - 1][i] = __ldcg(row + pos[i]);
+              }
+            }
+#pragma unroll
+            for (int sg = 1; sg < kDecMaxSegments; ++sg) {
+              if (sg > n_smem && sg < nseg) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  a[4 * i] += v[sg - 1][i].x;
+                  a[4 * i + 1] += v[sg - 1][i].y;
+                  a[4 * i + 2] += v[sg - 1][i].z;
+                  a[4 * i + 3] += v[sg - 1][i].w;
+                }
               }
             }
           }

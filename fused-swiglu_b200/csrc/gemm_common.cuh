@@ -207,6 +207,7 @@ __device__ __forceinline__ void drain_chunk(const GemmParams& p, uint32_t warp_s
 
 // This CTA's TMEM accumulator: `taddr` already carries the warp's lane field and the stage offset.
 struct TmemSource {
+  static constexpr bool kAsync = true;   // load() returns before the registers are written; wait() completes it
   uint32_t taddr;
   // n = 16 or 32 raw accumulator columns starting at column a0 -> r[0, n); asynchronous until wait()
   __device__ __forceinline__ void load(int a0, int n, uint32_t (&r)[32]) const {
@@ -231,6 +232,7 @@ __device__ __forceinline__ float4* partial_group(float* block, int a0, int row) 
 
 // Sum of `nseg` partial blocks in index order (fixed order: results do not depend on arrival order).
 struct PartialSource {
+  static constexpr bool kAsync = false;  // load() sums the blocks before it returns
   float* first_block;      // block of segment 0 of this tile, for this CTA's rank
   long long seg_stride;    // floats between consecutive segments' blocks
   int nseg;
@@ -274,6 +276,19 @@ __device__ __forceinline__ void store_partial_row(uint32_t taddr, float* block, 
   }
 }
 
+// Tell the compiler that r was (re)written here.  An asynchronous accumulator load names its destination
+// registers long before they hold data; placed right after the wait that completes the load, this keeps every
+// use of r behind that wait.
+__device__ __forceinline__ void written_by_now(uint32_t (&r)[32]) {
+  asm volatile(""
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                 "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                 "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------
 // The epilogue of one unit of work, for one epilogue warp (32 rows starting at row0; thread = row).
 // `width` output columns starting at col_base; accumulator columns as laid out by the mode.
@@ -291,16 +306,57 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams& p, const Source&
   constexpr int kPiecesPerChunk = kOutF32 ? 1 : 2;
   constexpr int kSegsPerPiece = kOutF32 ? 8 : 4;  // 32 columns
   int piece = 0, chunk_col0 = col_base, chunk_segs = 0;
+
+  // Raw accumulator values of the piece of output columns [c0, c0 + 32):
+  //   plain        a = accumulator columns c0 ...
+  //   split        a = gate columns c0 ..., b = up columns width + c0 ...
+  //   interleaved  a, b = accumulator columns 2 c0 ... and 2 c0 + 32 ... (column 2j = up, 2j + 1 = gate)
+  // Always 32 columns per request: a piece of 16 (odd width) reads 16 columns it does not use, which lie
+  // inside the same accumulator (widths are multiples of 16 and below the full width whenever that happens).
+  auto fetch = [&](int c0, int ncols, uint32_t (&a)[32], uint32_t (&b)[32]) {
+    const int n = Source::kAsync ? 32 : ncols;
+    if constexpr (kMode == kPlain) {
+      src.load(c0, n, a);
+    } else if constexpr (kMode == kGatedSplit) {
+      src.load(c0, n, a);
+      src.load(width + c0, n, b);
+    } else {
+      src.load(2 * c0, 32, a);
+      if (Source::kAsync || ncols == 32) {
+        src.load(2 * c0 + 32, 32, b);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) b[i] = 0u;
+      }
+    }
+  };
+  auto complete = [&](uint32_t (&a)[32], uint32_t (&b)[32]) {
+    src.wait();
+    if constexpr (Source::kAsync) {
+      written_by_now(a);
+      if constexpr (kMode != kPlain) written_by_now(b);
+    }
+  };
+
+  // With an asynchronous source the request for the next piece is in flight while this piece is converted,
+  // staged and stored; the registers it will land in are not touched until the wait at the end of the
+  // iteration (no value crosses the loop's back edge before it is complete).
+  uint32_t ra[32], rb[32];
+  if constexpr (Source::kAsync) {
+    fetch(0, min(32, width), ra, rb);
+    complete(ra, rb);
+  }
 #pragma unroll 1
   for (int c0 = 0; c0 < width; c0 += 32) {
     if (col_base + c0 >= p.n_out) break;  // warp-uniform: the rest of the tile is past the edge
     const int ncols = min(32, width - c0);  // 32, or 16 for the last piece of an odd width
     float v[32];
+    // plain mode: residual row segment first, so that its latency overlaps the accumulator read (ordinary
+    // loads: the residual may be the output buffer itself; a warp reads a chunk's elements before it writes them)
+    uint4 res[4];
+    bool with_res = false;
     if constexpr (kMode == kPlain) {
-      // residual row segment first, so that its latency overlaps the accumulator read (ordinary loads:
-      // the residual may be the output buffer itself; a warp reads a chunk's elements before it writes them)
-      uint4 res[4];
-      const bool with_res = p.residual != nullptr && row < p.M;
+      with_res = p.residual != nullptr && row < p.M;
       if (with_res) {
         const __nv_bfloat16* rrow =
             reinterpret_cast<const __nv_bfloat16*>(p.residual) + static_cast<long long>(row) * p.ld_res + col_base + c0;
@@ -310,11 +366,14 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams& p, const Source&
           if (8 * i < ncols && col_base + c0 + 8 * i < p.n_out) res[i] = *(reinterpret_cast<const uint4*>(rrow) + i);
         }
       }
-      uint32_t r[32];
-      src.load(c0, ncols, r);
-      src.wait();
+    }
+    if constexpr (!Source::kAsync) {
+      fetch(c0, ncols, ra, rb);
+      complete(ra, rb);
+    }
+    if constexpr (kMode == kPlain) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(ra[i]);
       if (with_res) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -327,28 +386,21 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams& p, const Source&
         }
       }
     } else if constexpr (kMode == kGatedSplit) {
-      uint32_t g[32], u[32];
-      src.load(c0, ncols, g);           // gate columns [0, width)
-      src.load(width + c0, ncols, u);   // up columns [width, 2 width)
-      src.wait();
 #pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = silu_mul(rs * __uint_as_float(g[i]), rs * __uint_as_float(u[i]));
+      for (int i = 0; i < 32; ++i) v[i] = silu_mul(rs * __uint_as_float(ra[i]), rs * __uint_as_float(rb[i]));
     } else {
-      // accumulator column 2j = up (linear), 2j+1 = gate (SiLU)
-      uint32_t lo[32], hi[32];
-      src.load(2 * c0, 32, lo);
-      if (ncols == 32) {
-        src.load(2 * c0 + 32, 32, hi);
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) hi[i] = 0u;
-      }
-      src.wait();
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        v[i] = silu_mul(rs * __uint_as_float(lo[2 * i + 1]), rs * __uint_as_float(lo[2 * i]));
-        v[16 + i] = silu_mul(rs * __uint_as_float(hi[2 * i + 1]), rs * __uint_as_float(hi[2 * i]));
+        v[i] = silu_mul(rs * __uint_as_float(ra[2 * i + 1]), rs * __uint_as_float(ra[2 * i]));
+        v[16 + i] = silu_mul(rs * __uint_as_float(rb[2 * i + 1]), rs * __uint_as_float(rb[2 * i]));
       }
+    }
+    uint32_t na[32], nb[32];
+    if constexpr (Source::kAsync) {
+      // the next piece (or, at the end, this one again: the request is unconditional so that nothing but the
+      // staging code sits between it and its wait)
+      const bool more = c0 + 32 < width && col_base + c0 + 32 < p.n_out;
+      fetch(more ? c0 + 32 : c0, 32, na, nb);
     }
     if (piece == 0) {
       chunk_col0 = col_base + c0;
@@ -359,6 +411,14 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams& p, const Source&
     if (++piece == kPiecesPerChunk) {
       drain_chunk<kOutF32>(p, warp_stage, lane, row0, chunk_col0, chunk_segs);
       piece = 0;
+    }
+    if constexpr (Source::kAsync) {
+      complete(na, nb);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        ra[i] = na[i];
+        if constexpr (kMode != kPlain) rb[i] = nb[i];
+      }
     }
   }
   if (piece != 0) drain_chunk<kOutF32>(p, warp_stage, lane, row0, chunk_col0, chunk_segs);

@@ -137,6 +137,37 @@ def test_mlp_matches_pipeline_oracle(fsw, cuda_dev, M, d, F):
     assert m2["rel_fro"] <= REL_FRO_GRADED and m2["scaled_max_abs"] <= SCALED_MAX_ABS, m2
 
 
+@pytest.mark.parametrize("M,d,F", [(16, 4096, 14336), (33, 4096, 14336), (64, 4096, 14336), (64, 128, 16384),
+                                   (40, 520, 4104)])
+def test_small_batch_reduction_paths_agree_bitwise(fsw, cuda_dev, M, d, F):
+    """The small-batch kernel combines the k-ranges of a row-block of W_down either from the workspace or from
+    copies of the partial tiles in shared memory (bulk copies into the idle rings; what does not fit stays in
+    the workspace).  Same values, same order: the outputs must be identical, with and without a residual and
+    in both output types; (64, 128, 16384) has more ranges per row-block than shared memory holds."""
+    x, wg, wu, wd = fsw.inputs.make_mlp_inputs(M, d, F, seed=21)
+    args = [t.to(cuda_dev) for t in (x, wg, wu, wd)]
+    res = torch.randn((M, d), generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).to(cuda_dev)
+    outs = {}
+    for mode in ("0", "1"):
+        old = os.environ.get("FSWIGLU_DECODE_SMEMRED")
+        os.environ["FSWIGLU_DECODE_SMEMRED"] = mode
+        try:
+            outs[mode] = (fsw.ops.fused_swiglu_mlp_bf16(*args), fsw.ops.fused_swiglu_mlp_bf16(*args, residual=res),
+                          fsw.ops.fused_swiglu_mlp_bf16(*args, out_dtype=torch.float32))
+            healthy(fsw)
+        finally:
+            if old is None:
+                os.environ.pop("FSWIGLU_DECODE_SMEMRED", None)
+            else:
+                os.environ["FSWIGLU_DECODE_SMEMRED"] = old
+    for a, b in zip(outs["0"], outs["1"]):
+        assert torch.equal(a, b)
+    default = fsw.ops.fused_swiglu_mlp_bf16(*args)
+    assert torch.equal(default, outs["0"][0])
+    m = orc.error_metrics(f32(default), orc.mlp_fp32(*[f32(t) for t in (x, wg, wu, wd)]))
+    assert m["rel_fro"] <= REL_FRO_GRADED and m["scaled_max_abs"] <= SCALED_MAX_ABS, m
+
+
 # ------------------------------------------------------------------ the benchmark configurations
 def test_config1_full_size_within_published_tolerance(fsw, cuda_dev):
     """Configuration 1 (M=512, d=1024, F=2816): whole output vs the fp32 expression,
