@@ -68,9 +68,10 @@ NOMINAL_HBM_GBS = 8000.0
 NOMINAL_BF16_TFLOPS = 2250.0
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from `ncu` captures of one
-# launch at the full workload size (profiles/): two-SM gate-up GEMM at the 7B prefill shape; small-batch
-# kernel at M = 16 (the other small-batch sizes stream the same weights).
-NCU_TRAFFIC_BYTES = {"c2_llama2_7b_prefill": 260.40e6 + 84.79e6, "c3_llama3_8b_decode_m16": 357.20e6 + 4.04e6}
+# launch at the full workload size (profiles/): the gate-up GEMM at the 70B shape (512-row two-SM kernel) and at
+# the 7B prefill shape (256-row two-SM kernel); small-batch kernel at M = 16 (the other small-batch sizes
+# stream the same weights).
+NCU_TRAFFIC_BYTES = {"c4_llama3_70b_prefill": 8079.7e6 + 468.7e6, "c2_llama2_7b_prefill": 260.40e6 + 84.79e6, "c3_llama3_8b_decode_m16": 357.20e6 + 4.04e6}
 PARITY_REL_FRO = 5e-3
 PARITY_SCALED_MAX_ABS = 8e-3
 
@@ -270,12 +271,14 @@ def parity_record(out, x, full_host, world, dist_mod, dev):
     return rec
 
 
-def kernel_name(M, n_out, tile, sms, gated):
-    pairs = ((M + 255) // 256) * ((n_out + tile - 1) // tile)
-    two_sm = M > 128 and pairs >= sms // 2 and os.environ.get("FSWIGLU_PAIR", "1")[:1] != "0"
+def kernel_name(M, n_out, K, gated):
+    """Name of the tiled kernel the library takes for this problem (asked from the library itself)."""
+    from fused_swiglu_b200 import capi
+    which = int(capi.lib.fswiglu_plan_kernel(M, n_out, K, 1 if gated else 0))
     mode = "gated-split" if gated else "plain"
-    return (f"gemm_pair_kernel<{mode}> (two-SM tcgen05, cta_group::2)" if two_sm
-            else f"gemm_tcgen05_kernel<{mode}> (one-SM tcgen05)")
+    return {0: f"gemm_tcgen05_kernel<{mode}> (one-SM tcgen05)",
+            1: f"gemm_pair_kernel<{mode}> (two-SM tcgen05, cta_group::2, 256-row tiles)",
+            2: f"gemm_quad_kernel<{mode}> (two-SM tcgen05, cta_group::2, 512-row tiles)"}.get(which, f"unknown ({which})")
 
 
 def tensor_roofline(name, rows, d, Fl, gateup_ms, n_launches, region_ms, sms, world, clocks=None):
@@ -293,7 +296,7 @@ def tensor_roofline(name, rows, d, Fl, gateup_ms, n_launches, region_ms, sms, wo
     frac = achieved / peak
     assert frac <= 1.2, f"roofline fraction {frac:.2f} is not a measurement (flops and time of different launches?)"
     traffic = NCU_TRAFFIC_BYTES.get(name) if world == 1 else None
-    return {"bound": "tensor", "kernel": kernel_name(rows, Fl, 128, sms, True) + ": gate-up + SiLU*up",
+    return {"bound": "tensor", "kernel": kernel_name(rows, Fl, d, True) + ": gate-up + SiLU*up",
             "achieved": achieved, "peak": peak, "unit": UNIT, "frac": frac, "traffic": traffic,
             "peak_source": f"{peak_src} {'sustained' if sustained else 'burst'} cuBLAS bf16",
             "frac_of_burst_peak": achieved / peaks["bf16_tflops"],
@@ -397,9 +400,9 @@ def run_single_prefill(name, args, dev, stream, local_rank, with_parity, with_su
     rec = {"workload": name, "value": flops_mlp(M, d, F) / (ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms,
            "steps": args.steps, "tokens_per_s": M / (ms * 1e-3),
            "roofline": tensor_roofline(name, M, d, F, gu_ms, len(w.events), total_ms, sms, 1, sampler.summary()),
-           "kernels": {"gate_up": {"kernel": kernel_name(M, F, 128, sms, True), "ms": gu_ms,
+           "kernels": {"gate_up": {"kernel": kernel_name(M, F, d, True), "ms": gu_ms,
                                    "tflops": 4.0 * M * d * F / (gu_ms * 1e-3) / 1e12},
-                       "down": {"kernel": kernel_name(M, d, 256, sms, False), "ms": dn_ms,
+                       "down": {"kernel": kernel_name(M, d, F, False), "ms": dn_ms,
                                 "tflops": 2.0 * M * d * F / (dn_ms * 1e-3) / 1e12}},
            "gpu_launches": int(launches), "clocks": sampler.summary()}
     clk = rec["clocks"].get("sm_mhz")

@@ -470,38 +470,40 @@ int launch_gemm_pair(const DeviceState& st, const void* a, int64_t lda, const vo
   return cudaGetLastError() == cudaSuccess ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
 }
 
-// 512-row tiles (gemm_quad_sm100.cuh).  They move 0.75 x the operand bytes per flop through the SMs and fewer
-// through HBM, which under the power cap buys clock; but there is no second accumulator stage, and a wave is 74
-// tiles of 512 x 256 outputs, so a partly filled last wave costs more.  Measured on B200 in 0.6 s loops
-// (same process, results bit-identical): down projection at the 70B shape 2.85 ms against 2.98-3.09 ms
-// (1352 against 1245-1291 TF/s), at the 7B shape 0.305 against 0.317 ms; gate-up at the 70B shape 5.90-5.98
-// against 5.87 ms and at the 7B shape 0.60 against 0.52-0.55 ms - the gated epilogue's exposed half and the
-// coarser wave eat the gain.  So: plain mode only, and only when the schedule's own arithmetic favours it with
-// a per-tile advantage of 6 % (the smaller of the two measured).  FSWIGLU_QUAD=0 never, =force always (tests).
-constexpr double kQuadTileAdvantage = 0.06;
+// 512-row tiles (gemm_quad_sm100.cuh).  They move 0.75 x the operand bytes per flop through the SMs and half
+// the bytes through HBM, which under the power cap buys clock; but there is no second accumulator stage (the
+// tensor pipe idles while a tile's accumulators are drained), and a wave is 74 tiles of 512 x 256 outputs, so
+// a partly filled last wave costs more.  Measured on B200 in 0.3-0.6 s loops (same process, results
+// bit-identical), 512-row against 256-row kernel:
+//   70B shape   gate-up 5.73 against 5.79-5.83 ms (1344 / 1325 TF/s)   down 2.75 against 2.97 ms (1397 / 1294)
+//   7B shape    gate-up 0.571 against 0.511-0.527 ms                   down 0.291 against 0.308-0.311 ms
+// Both kernels' times fit  waves x tile cost  with, in units of a 256-row tile's main loop, a 512-row tile
+// costing 2 x 0.905 + 18.5 / k-blocks (the drained-accumulator gap is worth about 18 k-blocks) and the
+// 256-row kernel's partly filled last wave 0.85 (half-width units) or 1.  The 512-row kernel is taken when
+// that arithmetic favours it by more than 1 %.  (At the 7B down shape the model says no although the loops
+// above say yes: in short bursts, where power does not set the clock, the coarser wave loses.)
+// FSWIGLU_QUAD=0 never, =force always (tests).
 int quad_mode() {  // 0 never, 1 automatic, 2 always
   const char* env = std::getenv("FSWIGLU_QUAD");
   if (env == nullptr || env[0] == '\0') return 1;
   if (env[0] == '0') return 0;
   return (env[0] == 'f' || env[0] == 'F') ? 2 : 1;
 }
-bool use_quad_kernel(const DeviceState& st, const GemmParams& p, int tile_n, bool gated) {
+bool use_quad_kernel(const DeviceState& st, const GemmParams& p, int tile_n) {
   const int mode = quad_mode();
   if (mode == 0 || effective_ctas(st) < 2 || pair_mode() == 0) return false;
   if (mode == 2) return true;
-  if (gated) return false;
   if (pair_mode() == 2) return false;     // the 256-row kernel was asked for by name
   if (p.scatter_world > 0) return false;  // row slabs of a tensor-parallel step: few waves each
   const int64_t clusters = effective_ctas(st) / 2;
   const int64_t n_tiles = (p.n_out + tile_n - 1) / tile_n;
   const int64_t quad = ((p.M + 511) / 512) * n_tiles, pair = ((p.M + 255) / 256) * n_tiles;
   if (pair < clusters) return false;  // below one wave the one-SM kernel takes over
-  // cost in units of one 256-row tile's main loop
-  const double quad_cost = 2.0 * static_cast<double>((quad + clusters - 1) / clusters) * (1.0 - kQuadTileAdvantage);
+  const double num_kb = static_cast<double>((p.K + kBlockK - 1) / kBlockK);
+  const double quad_cost = static_cast<double>((quad + clusters - 1) / clusters) * (2.0 * 0.905 + 18.5 / num_kb);
   const int64_t rem = pair % clusters;
-  // the 256-row kernel's last wave: half-width units (about 0.6 of a tile's time) when it is at most half full
-  const double pair_cost = static_cast<double>(pair / clusters) + (rem == 0 ? 0.0 : (2 * rem <= clusters ? 0.6 : 1.0));
-  return quad_cost < pair_cost;
+  const double pair_cost = static_cast<double>(pair / clusters) + (rem == 0 ? 0.0 : (2 * rem <= clusters ? 0.85 : 1.0));
+  return quad_cost < 0.99 * pair_cost;
 }
 
 // Raster for 512-row tiles: the same reasoning as pick_pair_group_m with twice the rows per M-tile.
@@ -574,7 +576,7 @@ int gateup_impl(DeviceState& st, const void* x, int64_t ldx, const void* w0, int
   p.vec_ok = (aligned16(h) && ldh % 8 == 0) ? 1 : 0;
   p.status = st.status;
   p.row_scale = row_scale;
-  if (use_quad_kernel(st, p, 128, true)) {
+  if (use_quad_kernel(st, p, 128)) {
     return interleaved ? launch_gemm_quad<kGatedInterleaved, false>(st, x, ldx, w0, nullptr, ldw, 2 * F, p, stream)
                        : launch_gemm_quad<kGatedSplit, false>(st, x, ldx, w0, w_up, ldw, F, p, stream);
   }
@@ -632,7 +634,7 @@ int down_impl(DeviceState& st, const void* h, int64_t ldh, const void* w_down, i
   p.status = st.status;
   p.residual = residual;
   p.ld_res = ldr;
-  if (use_quad_kernel(st, p, 256, false)) {
+  if (use_quad_kernel(st, p, 256)) {
     return f32 ? launch_gemm_quad<kPlain, true>(st, h, ldh, w_down, nullptr, ldw, d, p, stream)
                : launch_gemm_quad<kPlain, false>(st, h, ldh, w_down, nullptr, ldw, d, p, stream);
   }
@@ -1378,6 +1380,19 @@ const char* fswiglu_status_string(int status) {
       return "M * F * 2 bytes exceeds the 32 MiB scratch built into fswiglu_mlp_bf16_static";
     default: return "unknown status";
   }
+}
+
+int fswiglu_plan_kernel(int64_t M, int64_t n_out, int64_t K, int gated) {
+  if (M < 0 || n_out <= 0 || K <= 0) return FSWIGLU_ERR_SHAPE;
+  DeviceState* st = nullptr;
+  if (int rc = device_state(&st)) return rc;
+  GemmParams p = {};
+  p.M = static_cast<int>(M);
+  p.n_out = static_cast<int>(n_out);
+  p.K = static_cast<int>(K);
+  const int tile_n = gated ? 128 : 256;
+  if (use_quad_kernel(*st, p, tile_n)) return 2;
+  return use_pair_kernel(*st, M, n_out, tile_n) ? 1 : 0;
 }
 
 const char* fswiglu_version(void) { return "0.2.0"; }

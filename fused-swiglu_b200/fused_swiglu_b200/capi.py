@@ -58,6 +58,7 @@ SIGNATURES = {
     "fswiglu_test_expire_next_wait": (None, [_int]),
     "fswiglu_set_decode_trace": (None, [_vp]),
     "fswiglu_status_string": (ctypes.c_char_p, [_int]),
+    "fswiglu_plan_kernel": (ctypes.c_int, [ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int]),
     "fswiglu_version": (ctypes.c_char_p, []),
     "fswiglu_launch_count": (ctypes.c_uint64, []),
 }

@@ -302,6 +302,15 @@ void fswiglu_set_decode_trace(void* device_buffer);
 /* Human-readable name of a status code returned by this library. */
 const char* fswiglu_status_string(int status);
 
+/*
+ * Which tiled GEMM kernel a launch of the given problem takes on the current device, with the current SM
+ * budget and environment: 0 = one-SM kernel (128-row tiles), 1 = two-SM kernel with 256-row tiles, 2 = two-SM
+ * kernel with 512-row tiles; negative = status code.  gated != 0: gate-up problem (n_out = F output columns,
+ * K = d); gated == 0: plain problem (down projection: n_out = d, K = F).  The small-batch path (M <= 64 through
+ * fswiglu_mlp_bf16) is not covered.  For launch accounting, labels and tests; no reference counterpart.
+ */
+int fswiglu_plan_kernel(int64_t M, int64_t n_out, int64_t K, int gated);
+
 /* Library version, "major.minor.patch". */
 const char* fswiglu_version(void);
 

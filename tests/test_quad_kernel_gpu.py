@@ -174,7 +174,13 @@ def test_70b_shape_takes_the_512_row_kernel_and_equals_the_256_row_kernel(fsw, c
     """At M = d = 8192, F = 28672 the host picks the 512-row kernel for both GEMMs by itself (49 and 7 waves of
     its tiles); the whole output must equal the 256-row kernel's, bit for bit."""
     x, wg, wu, wd = (t.to(cuda_dev) for t in fsw.inputs.make_config_inputs("c4_llama3_70b_prefill"))
-    ws = fsw.ops.mlp_workspace(x.size(0), x.size(1), wg.size(0), cuda_dev)
+    M, d, F = x.size(0), x.size(1), wg.size(0)
+    plan = fsw.capi.lib.fswiglu_plan_kernel
+    assert plan(M, F, d, 1) == 2 and plan(M, d, F, 0) == 2
+    assert plan(4096, 11008, 4096, 1) == 1 and plan(300, 1096, 520, 1) == 0  # 7B gate-up; a small problem
+    with env(FSWIGLU_QUAD="0"):
+        assert plan(M, F, d, 1) == 1
+    ws = fsw.ops.mlp_workspace(M, d, F, cuda_dev)
     out = fsw.ops.fused_swiglu_mlp_bf16(x, wg, wu, wd, workspace=ws)
     with env(FSWIGLU_QUAD="0"):
         ref = fsw.ops.fused_swiglu_mlp_bf16(x, wg, wu, wd, workspace=ws)

@@ -40,15 +40,15 @@ def env(**kv):
                 os.environ[k] = v
 
 
-@pytest.mark.parametrize("kernel", ["one_sm", "two_sm", "small_batch"])
+@pytest.mark.parametrize("kernel", ["one_sm", "two_sm", "two_sm_512", "small_batch"])
 def test_a_wait_that_runs_out_is_reported_and_leaves_the_device_usable(cuda_dev, kernel):
     import fused_swiglu_b200 as fsw
 
     capi = fsw.capi
     M = 4 if kernel == "small_batch" else 300
     x, wg, wu, wd = (t.to(cuda_dev) for t in fsw.inputs.make_mlp_inputs(M, 520, 1096, seed=0))
-    pair = "force" if kernel == "two_sm" else "0"
-    with env(FSWIGLU_PAIR=pair):
+    pair = {"two_sm": "force", "two_sm_512": ""}.get(kernel, "0")
+    with env(FSWIGLU_PAIR=pair, FSWIGLU_QUAD="force" if kernel == "two_sm_512" else "0"):
         want = fsw.ops.fused_swiglu_mlp_bf16(x, wg, wu, wd)
         torch.cuda.synchronize()
         assert capi.device_status() == 0
