@@ -538,6 +538,8 @@ int launch_gemm_quad(const DeviceState& st, const void* a, int64_t lda, const vo
     const int v = std::atoi(env);
     if (v >= 1) p.group_m = std::min(v, p.num_m_tiles);
   }
+  if (const char* env = std::getenv("FSWIGLU_HINT_A")) p.hint_a = std::atoi(env);  // experiments only
+  if (const char* env = std::getenv("FSWIGLU_HINT_B")) p.hint_b = std::atoi(env);
   int rc;
   CUtensorMap ma, mb0, mb1;
   if ((rc = encode_map(&ma, a, p.M, p.K, lda, 128))) return rc;

@@ -107,6 +107,7 @@ gemm_quad_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       bool alive = true;
       bool withhold = p.withhold_one_copy != 0 && blockIdx.x == 0;  // one-shot, leader of the first pair
       const uint32_t stage_tx_bytes = kQuadABytes + static_cast<uint32_t>(b_half_rows) * (kBlockK * 2);
+      const uint64_t pol_a = l2_policy_of(p.hint_a), pol_b = l2_policy_of(p.hint_b);
       for (int tile = cluster_id; tile < num_tiles && alive; tile += num_clusters) {
         const TileCoord tc = tile_coord(tile, p);
         const int m0 = tc.m_tile * kQuadTileRows + static_cast<int>(rank) * 256;
@@ -130,9 +131,21 @@ gemm_quad_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           // one barrier per stage, in the leader: it expects the bytes of both CTAs
           if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2u * stage_tx_bytes);
           const uint32_t leader_full = map_to_cta(full_bar(stage), 0);
-          tma_load_2d_pair(a_dst, &map_a, leader_full, kb * kBlockK, m0);
-          tma_load_2d_pair(a_dst + kATileBytes, &map_a, leader_full, kb * kBlockK, m0 + 128);
-          if (!withhold) tma_load_2d_pair(a_dst + kQuadABytes, bmap, leader_full, kb * kBlockK, b_row);
+          // no residency class: the plain load (the hardware's default policy), else the load with a hint
+          if (p.hint_a == kL2Default) {
+            tma_load_2d_pair(a_dst, &map_a, leader_full, kb * kBlockK, m0);
+            tma_load_2d_pair(a_dst + kATileBytes, &map_a, leader_full, kb * kBlockK, m0 + 128);
+          } else {
+            tma_load_2d_pair_hint(a_dst, &map_a, leader_full, kb * kBlockK, m0, pol_a);
+            tma_load_2d_pair_hint(a_dst + kATileBytes, &map_a, leader_full, kb * kBlockK, m0 + 128, pol_a);
+          }
+          if (!withhold) {
+            if (p.hint_b == kL2Default) {
+              tma_load_2d_pair(a_dst + kQuadABytes, bmap, leader_full, kb * kBlockK, b_row);
+            } else {
+              tma_load_2d_pair_hint(a_dst + kQuadABytes, bmap, leader_full, kb * kBlockK, b_row, pol_b);
+            }
+          }
           withhold = false;
           issued_mask |= 1u << stage;
           last_parity_mask = (last_parity_mask & ~(1u << stage)) | (phase << stage);
