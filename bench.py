@@ -770,9 +770,7 @@ def run_tensor_parallel(args, rank, local_rank, world):
     # ----------------------------- end to end through host buffers -------------------------------
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
     x_host = x.cpu().pin_memory()
-    rows_per = (M + world - 1) // world
-    r0, r1 = min(M, rank * rows_per), min(M, (rank + 1) * rows_per)
-    out_host = torch.empty((r1 - r0, d), dtype=torch.bfloat16).pin_memory()
+    out_host = torch.empty((sum(g1 - g0 for g0, g1 in tp.owned_rows(M)), d), dtype=torch.bfloat16).pin_memory()
     for _ in range(3):
         tp.forward_from_host(x_host, out_host)
     barrier()
@@ -804,7 +802,7 @@ def run_tensor_parallel(args, rank, local_rank, world):
             "roofline": roofline,
             "e2e": {"value": flops_mlp(M, d, F) / e2e_s / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": M * d * 2, "ms_per_step": e2e_s * 1e3, "steps": e2e_steps,
-                    "api": "TensorParallelSwiGLU.forward_from_host (1/N of x over PCIe per rank, rest over NVLink)"},
+                    "api": "TensorParallelSwiGLU.forward_from_host (1/N of x over PCIe per rank, rest over NVLink; copies of slab i+1 and of the finished rows of slab i-1 overlap the GEMMs of slab i)"},
             "gpu_launches": int(launches), "clocks": sampler.summary(),
         }
         if parity is not None:

@@ -107,6 +107,41 @@ def plan_slabs(M: int, d: int, F_local: int, world: int, ctas: int) -> list:
     return best_rows
 
 
+_PCIE_BYTES_PER_US = 5.0e4   # host link per GPU and direction (measured: about 53 GB/s)
+
+
+def _host_timeline_us(rows_list, d, F_local, world, ctas) -> float:
+    """Step time when every slab's rows come from and go back to host memory, 1/world of them per rank, on copy
+    streams beside the GEMMs: in-copies queue one behind the other, a slab computes once its rows are in, a
+    rank's finished rows leave after the slab's reduction."""
+    in_end = compute_end = comm_end = out_end = 0.0
+    for rows in rows_list:
+        io = rows / world * d * 2 / _PCIE_BYTES_PER_US
+        in_end += io + rows / world * d * 2 * (world - 1) / _NVLINK_BYTES_PER_US + _BARRIER_US
+        compute_end = max(compute_end, in_end) + _slab_compute_us(rows, d, F_local, ctas)
+        out_bytes = rows / world * d * 2 * (world - 1)
+        comm_end = max(compute_end, comm_end) + _BARRIER_US + out_bytes / _NVLINK_BYTES_PER_US
+        out_end = max(comm_end, out_end) + io
+    return out_end
+
+
+def plan_host_slabs(M: int, d: int, F_local: int, world: int, ctas: int) -> list:
+    """Slab heights for the host-buffer step of the push mode: as plan_slabs, but the first slab's copy in and
+    the last slab's copy out are exposed, so more and more equal slabs win than in the device-resident step."""
+    if M <= 1024 or world == 1:
+        return [M]
+    best_rows, best_t = [M], _host_timeline_us([M], d, F_local, world, ctas)
+    for R in range(256, M, 256):
+        n = -(-M // R)
+        if n > 8:
+            continue
+        rows = [R] * (n - 1) + [M - R * (n - 1)]
+        t = _host_timeline_us(rows, d, F_local, world, ctas)
+        if t < best_t:
+            best_rows, best_t = rows, t
+    return best_rows
+
+
 class TensorParallelSwiGLU:
     """Rank-local shard of the MLP plus the collective that completes the forward.
 
@@ -144,6 +179,8 @@ class TensorParallelSwiGLU:
         self.device = w_gate_shard.device
         self.F_local, self.d = w_gate_shard.shape
         self._bufs = {}
+        self._scratch = None
+        self._recv_hdl = self._out_hdl = None
         self._cuda = self.device.type == "cuda"
         self._comm_stream = torch.cuda.Stream(device=self.device, priority=-1) if self._cuda else None
         # reduce + broadcast kernel (push mode): 128 CTAs of 128 threads, one beside each GEMM CTA on most SMs.
@@ -151,6 +188,8 @@ class TensorParallelSwiGLU:
         # outlasts the second slab's GEMMs), 128 CTAs 1.264 ms.
         self._reduce_ctas = reduce_ctas if reduce_ctas > 0 else 128
         self._xin = None
+        self._copy_streams = None
+        self._bounds_cache = {}
         # explicit slab heights (rows), e.g. [3840, 3840, 512]; every slab but the last must be a
         # multiple of 8 * world.  None: n_slabs equal slabs.
         self.slab_rows = list(slab_rows) if slab_rows else None
@@ -196,7 +235,18 @@ class TensorParallelSwiGLU:
         return cls(g.to(device), u.to(device), dn.to(device), group=group, **kw)
 
     # slab r0:r1 boundaries; with rs_ag every slab must split evenly over the ranks
-    def slab_bounds(self, M: int):
+    def slab_bounds(self, M: int, host: bool = False):
+        """Row slabs of a step over M rows; host=True: of the host-buffer step (forward_from_host), whose
+        planned slabs also weigh the exposed copies."""
+        # planned once per batch size: the planner walks a cost model over candidate splits, which costs
+        # milliseconds of host time at large M, and this is called on the critical path of every step
+        key = (M, tuple(self.slab_rows or ()), self.n_slabs, self.mode, host)
+        cached = self._bounds_cache.get(key)
+        if cached is None:
+            cached = self._bounds_cache[key] = self._plan_bounds(M, host)
+        return list(cached)
+
+    def _plan_bounds(self, M: int, host: bool):
         quantum = self.world * 8 if self.mode in ("rs_ag", "push") else 1
         if self.slab_rows and sum(self.slab_rows) == M and all(r > 0 for r in self.slab_rows) and \
                 all(r % quantum == 0 for r in self.slab_rows[:-1]):
@@ -207,7 +257,8 @@ class TensorParallelSwiGLU:
             return bounds
         if self.mode == "push" and self.world > 1 and self.n_slabs_auto and 128 % quantum == 0:
             bounds, r0 = [], 0
-            for r in plan_slabs(M, self.d, self.F_local, self.world, self._gemm_ctas):
+            planner = plan_host_slabs if host else plan_slabs
+            for r in planner(M, self.d, self.F_local, self.world, self._gemm_ctas):
                 bounds.append((r0, r0 + r))
                 r0 += r
             return bounds
@@ -222,22 +273,24 @@ class TensorParallelSwiGLU:
             r0 = r1
         return bounds
 
-    def _buffers(self, M: int):
-        key = M
+    def _buffers(self, M: int, bounds):
+        """Receive / output / workspace buffers of a step over these slabs (kept per slab plan: the symmetric
+        buffers are laid out slab by slab, each padded to a multiple of the world size)."""
+        key = (M, tuple(bounds))
         if key not in self._bufs:
             dev = self.device
             Mp = M
             if self.mode in ("rs_ag", "push"):
                 q = self.world
-                Mp = sum(((r1 - r0 + q - 1) // q * q) for r0, r1 in self.slab_bounds(M))
+                Mp = sum(((r1 - r0 + q - 1) // q * q) for r0, r1 in bounds)
+            handles = None
             if self.mode == "push" and self.world > 1:
                 import torch.distributed._symmetric_memory as symm_mem
 
                 grp = self.group if self.group is not None else dist.group.WORLD
                 partial = symm_mem.empty((Mp, self.d), dtype=torch.bfloat16, device=dev)  # receive buffer
                 out = symm_mem.empty((Mp, self.d), dtype=torch.bfloat16, device=dev)
-                self._recv_hdl = symm_mem.rendezvous(partial, grp)
-                self._out_hdl = symm_mem.rendezvous(out, grp)
+                handles = (symm_mem.rendezvous(partial, grp), symm_mem.rendezvous(out, grp))
             else:
                 partial = torch.empty((Mp, self.d), dtype=self.wire_dtype, device=dev)
                 out = torch.empty((Mp, self.d), dtype=torch.bfloat16, device=dev)
@@ -245,21 +298,32 @@ class TensorParallelSwiGLU:
             if self._cuda:
                 from . import ops
 
-                per = max(r1 - r0 for r0, r1 in self.slab_bounds(M))
+                per = max(r1 - r0 for r0, r1 in bounds)
                 ws = ops.mlp_workspace(per, self.d, self.F_local, dev)
-                self._scratch = ops.gemm_scratch(dev)
-            self._bufs = {key: (partial, out, ws)}
-        return self._bufs[key]
+                if self._scratch is None:
+                    self._scratch = ops.gemm_scratch(dev)
+            if len(self._bufs) >= 4:  # a handful of batch sizes / plans at most
+                self._bufs.pop(next(iter(self._bufs)))
+            self._bufs[key] = (partial, out, ws, handles)
+        partial, out, ws, handles = self._bufs[key]
+        if handles is not None:
+            self._recv_hdl, self._out_hdl = handles
+        return partial, out, ws
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        """x [M, d] replicated on every rank -> out [M, d] bf16, identical on every rank."""
+    def forward(self, x: torch.Tensor, slab_ready=None, slab_done=None, host_plan: bool = False) -> torch.Tensor:
+        """x [M, d] replicated on every rank -> out [M, d] bf16, identical on every rank.
+
+        push mode only: `slab_ready[i]` is an event the compute stream waits for before it touches the rows of
+        slab i of x; `slab_done(i, out_rows)` is called, with the reduction stream current, once this rank's own
+        rows of slab i (owned_rows) are final in `out_rows`.  forward_from_host uses both to overlap the host
+        copies with the GEMMs."""
         M = x.size(0)
         if M == 0:
             return torch.empty((0, self.d), dtype=torch.bfloat16, device=self.device)
-        partial, out, ws = self._buffers(M)
-        bounds = self.slab_bounds(M)
+        bounds = self.slab_bounds(M, host_plan)
+        partial, out, ws = self._buffers(M, bounds)
         if self.mode == "push" and self.world > 1:
-            return self._forward_push(x, partial, out, ws, bounds)
+            return self._forward_push(x, partial, out, ws, bounds, slab_ready, slab_done)
         compute = torch.cuda.current_stream(self.device) if self._cuda else None
         off = 0  # row offset in the (possibly padded) partial / out buffers
         for (r0, r1) in bounds:
@@ -313,18 +377,37 @@ class TensorParallelSwiGLU:
         return out[:M]
 
 
+    def owned_rows(self, M: int):
+        """The rows of the result this rank hands back in forward_from_host, as (first, end) ranges in order.
+        push mode: the rows it reduces, slab by slab (rank r owns the r-th 1/world of every slab); otherwise
+        the r-th 1/world of all rows."""
+        world, rank = self.world, self.rank
+        if world == 1 or self.mode != "push":
+            per = (M + world - 1) // world
+            return [(min(M, rank * per), min(M, (rank + 1) * per))]
+        ranges = []
+        for (r0, r1) in self.slab_bounds(M, host=True):
+            rpo = ((r1 - r0) + world - 1) // world
+            g0 = min(r1, r0 + rank * rpo)
+            ranges.append((g0, min(r1, g0 + rpo)))
+        return ranges
+
     def forward_from_host(self, x_host: torch.Tensor, out_host: torch.Tensor) -> None:
         """End-to-end step with host buffers.  x_host [M, d] is the (pinned) host copy of the replicated
-        input; out_host receives this rank's rows [rank*M/world, (rank+1)*M/world) of the result.
+        input; out_host receives this rank's rows of the result, the ranges owned_rows(M) one after the other.
 
-        Every rank copies only its 1/world row slice over PCIe, then the slices are exchanged over
-        NVLink (copy engines writing into the peers' symmetric input buffers), so the host link
-        carries M*d*2/world bytes per rank instead of M*d*2.  Returns when out_host is filled."""
+        Every rank copies only its own rows over PCIe and hands them to the peers over NVLink (copy engines
+        writing into the peers' symmetric input buffers), so the host link carries M*d*2/world bytes per rank
+        instead of M*d*2.  In push mode this goes slab by slab on a copy stream of its own: slab i+1 arrives
+        while slab i is in the GEMMs, and this rank's rows of slab i go back to the host as soon as its
+        reduction is done, while later slabs compute.  Returns when out_host is filled."""
         M = x_host.size(0)
         world, rank = self.world, self.rank
-        per = (M + world - 1) // world
-        r0, r1 = min(M, rank * per), min(M, (rank + 1) * per)
+        owned = self.owned_rows(M)
+        if sum(g1 - g0 for g0, g1 in owned) != out_host.size(0):
+            raise RuntimeError("out_host must hold exactly the rows of owned_rows(M)")
         if world == 1 or self.mode != "push":
+            (r0, r1), = owned
             x = x_host.to(self.device, non_blocking=True)
             out = self.forward(x)
             out_host.copy_(out[r0:r1], non_blocking=True)
@@ -339,16 +422,42 @@ class TensorParallelSwiGLU:
             peers = [hdl.get_buffer(p, (M, self.d), torch.bfloat16) for p in range(world)]
             self._xin = (xin, hdl, peers)
         xin, hdl, peers = self._xin
-        xin[r0:r1].copy_(x_host[r0:r1], non_blocking=True)           # PCIe: own slice only
-        for k in range(1, world):                                     # NVLink: slice to every peer
-            peers[(rank + k) % world][r0:r1].copy_(xin[r0:r1], non_blocking=True)
-        hdl.barrier(channel=1)                                        # all slices have landed here
-        out = self.forward(xin)
-        out_host.copy_(out[r0:r1], non_blocking=True)
-        hdl.barrier(channel=2)                                        # nobody overwrites xin while it is read
-        torch.cuda.current_stream(self.device).synchronize()
+        if self._copy_streams is None:
+            self._copy_streams = (torch.cuda.Stream(device=self.device), torch.cuda.Stream(device=self.device))
+        h2d, d2h = self._copy_streams
+        cur = torch.cuda.current_stream(self.device)
+        h2d.wait_stream(cur)
+        ready = []
+        with torch.cuda.stream(h2d):
+            for si, (g0, g1) in enumerate(owned):
+                if g1 > g0:
+                    xin[g0:g1].copy_(x_host[g0:g1], non_blocking=True)        # PCIe: own rows of this slab only
+                    for k in range(1, world):                                 # NVLink: to every peer
+                        peers[(rank + k) % world][g0:g1].copy_(xin[g0:g1], non_blocking=True)
+                hdl.barrier(channel=si % 8)                                   # all ranks' rows of slab si are here
+                ev = torch.cuda.Event()
+                ev.record(h2d)
+                ready.append(ev)
+        out_off = [0]
+        for g0, g1 in owned:
+            out_off.append(out_off[-1] + (g1 - g0))
 
-    def _forward_push(self, x, recv, out, ws, bounds):
+        def slab_done(si, out_rows):
+            n = owned[si][1] - owned[si][0]
+            if n <= 0:
+                return
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(self.device))
+            d2h.wait_event(ev)
+            with torch.cuda.stream(d2h):
+                out_host[out_off[si]:out_off[si] + n].copy_(out_rows[:n], non_blocking=True)
+
+        self.forward(xin, slab_ready=ready, slab_done=slab_done, host_plan=True)
+        hdl.barrier(channel=15)                                       # nobody overwrites xin while it is read
+        cur.wait_stream(d2h)
+        cur.synchronize()
+
+    def _forward_push(self, x, recv, out, ws, bounds, slab_ready=None, slab_done=None):
         """Reduce-scatter inside the down-GEMM epilogue (peer stores), then reduce + broadcast."""
         import ctypes
 
@@ -371,6 +480,8 @@ class TensorParallelSwiGLU:
                 xs = x[r0:r1]
                 h = ws[: rows * Fl * 2].view(torch.bfloat16).view(rows, Fl)
                 sp = ctypes.c_void_p(compute.cuda_stream)
+                if slab_ready is not None:
+                    compute.wait_event(slab_ready[si])
                 if self.trace is not None:
                     self.trace("gateup_begin", si, compute)
                 rc = lib.fswiglu_gateup_bf16_ex(vp(xs), xs.stride(0), vp(self.w_gate), self.w_gate.stride(0),
@@ -400,6 +511,8 @@ class TensorParallelSwiGLU:
                     capi.check(rc, "fswiglu_reduce_bcast_bf16")
                     if self.trace is not None:
                         self.trace("reduce_end", si, comm)
+                    if slab_done is not None:
+                        slab_done(si, out[off + rank * rpo:off + (rank + 1) * rpo])
                 off += rows_p
             with torch.cuda.stream(comm):
                 self._out_hdl.barrier(channel=0)  # every rank's result rows have landed everywhere

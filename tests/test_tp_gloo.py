@@ -61,6 +61,16 @@ def _worker(rank, world, port, mode, M, fail_rank, q):
         gathered = [torch.empty_like(out) for _ in range(world)]
         dist.all_gather(gathered, out)
         same = all(torch.equal(g, out) for g in gathered)
+        # the rows each rank hands back in the host-buffer step cover the result exactly once, in this mode and
+        # in the slab-wise ownership of the push mode (pure index arithmetic, no GPU needed)
+        push = TensorParallelSwiGLU.from_full(wg, wu, wd, torch.device("cpu"), n_slabs=3, mode="push",
+                                              local_partial=_oracle_partial, round_fn=_round)
+        for inst, rows in ((tp, M), (push, M), (push, 8192), (push, 777)):
+            mine = inst.owned_rows(rows)
+            everyone = [None] * world
+            dist.all_gather_object(everyone, mine)
+            covered = sorted(r for ranges in everyone for g0, g1 in ranges for r in range(g0, g1))
+            same = same and covered == list(range(rows))
         q.put((rank, "ok", m["rel_fro"], same, tuple(out.shape)))
     except Exception as e:  # noqa: BLE001
         q.put((rank, "error", repr(e)[:200], False, ()))

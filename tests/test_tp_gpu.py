@@ -79,12 +79,18 @@ def _worker(rank, world, port, mode, M, q):
         gathered = [torch.empty_like(out) for _ in range(world)]
         dist.all_gather(gathered, out)
         same = all(torch.equal(g, out) for g in gathered) and torch.equal(out, out2)
-        # host-buffer step: own slice over PCIe, the rest over NVLink, own slice of the result back
-        per = (M + world - 1) // world
-        r0, r1 = min(M, rank * per), min(M, (rank + 1) * per)
-        out_host = torch.empty((r1 - r0, out.size(1)), dtype=torch.bfloat16).pin_memory()
-        tp.forward_from_host(x.pin_memory(), out_host)
-        same = same and torch.equal(out_host, out[r0:r1].cpu())
+        # host-buffer step: own rows over PCIe, the rest over NVLink, own rows of the result back (push mode:
+        # slab by slab, overlapped with the GEMMs); twice, the second step re-uses every buffer
+        owned = tp.owned_rows(M)
+        want = torch.cat([out[g0:g1] for g0, g1 in owned]).cpu()
+        x_pinned = x.pin_memory()
+        for _ in range(2):
+            out_host = torch.zeros((want.size(0), out.size(1)), dtype=torch.bfloat16).pin_memory()
+            tp.forward_from_host(x_pinned, out_host)
+            same = same and torch.equal(out_host, want)
+        counts = [torch.zeros(1, dtype=torch.int64, device=dev) for _ in range(world)]
+        dist.all_gather(counts, torch.tensor([want.size(0)], dtype=torch.int64, device=dev))
+        same = same and sum(int(c.item()) for c in counts) == M  # the ranks' rows cover the result exactly once
         q.put((rank, "ok", m["rel_fro"], m["scaled_max_abs"], same, fsw.capi.device_status()))
     except Exception as e:  # noqa: BLE001
         q.put((rank, "error", repr(e)[:300], 0.0, False, -1))
