@@ -911,21 +911,64 @@ namespace {
 
 // Rows per slab of the host-buffer pipeline: large enough that each slab still fills the
 // machine (>= 1024 rows), small enough that the first copy in and the last copy out are short.
+// Measured at the 70B shape in one process (20 steps each, power-capped): equal 1024-row slabs 9.89-9.96 ms per
+// step, 1024-row slabs with 512-row first and last slab 9.89-9.91, equal 2048-row slabs 9.72-10.1, 2048-row slabs
+// with 512-row first and last slab 9.58-9.66 (the device-resident step: 8.7-8.9 ms): taller slabs fill the GEMM
+// waves better, short edge slabs expose less of the first copy in and the last copy out.
 int64_t host_slab_rows(int64_t M) {
-  int64_t rows = 1024;
+  int64_t rows = M >= 8192 ? 2048 : 1024;
+  if (const char* env = std::getenv("FSWIGLU_HOST_SLAB")) {  // experiments only: rows per slab
+    const int v = std::atoi(env);
+    if (v >= 128 && v % 128 == 0) rows = v;
+  }
   const int64_t min_rows = (M + kMaxHostSlabs - 1) / kMaxHostSlabs;
   if (rows < min_rows) rows = (min_rows + 127) / 128 * 128;
   if (rows > M) rows = M;
   return rows;
 }
 
-// Workspace of one slab's MLP call: the full slab and the ragged last slab may take different paths
-// (a last slab of <= 64 rows takes the small-batch kernel with its own partial tiles).
-size_t host_slab_workspace_bytes(int64_t M, int64_t d, int64_t F) {
+// Row slabs of the host-buffer pipeline.  The first slab's copy in and the last slab's copy out cannot overlap
+// any compute, so with enough rows those two slabs are half as tall as the rest (at the 70B shape: 0.15 ms
+// exposed at either end instead of 0.3 ms).  Returns the slab count; first[i] / rows[i] describe slab i.
+int host_slab_plan(int64_t M, int64_t* first, int64_t* rows) {
   const int64_t slab = host_slab_rows(M);
-  size_t bytes = fswiglu_workspace_bytes(slab, d, F);
-  const int64_t last = M % slab;
-  if (last != 0) bytes = std::max(bytes, fswiglu_workspace_bytes(last, d, F));
+  int n = 0;
+  int64_t r = 0;
+  auto push = [&](int64_t take) {
+    first[n] = r;
+    rows[n] = take;
+    r += take;
+    ++n;
+  };
+  bool short_edges = slab >= 1024 && slab % 1024 == 0 && M >= 4 * slab && M <= (kMaxHostSlabs - 4) * slab;
+  if (const char* env = std::getenv("FSWIGLU_HOST_EDGES")) {  // experiments only: 0 = equal slabs
+    if (env[0] == '0') short_edges = false;
+  }
+  if (!short_edges) {
+    while (r < M) push(M - r < slab ? M - r : slab);
+    return n;
+  }
+  const int64_t edge = 512, middle = M - 2 * edge;
+  int64_t n_mid = (middle + slab - 1) / slab;
+  int64_t rem = middle - (n_mid - 1) * slab;  // 1 .. slab rows in the last middle slab
+  if (rem < 256 && n_mid > 1) {               // too few rows for a slab of their own: the one before takes them
+    --n_mid;
+    rem += slab;
+  }
+  push(edge);
+  for (int64_t i = 0; i + 1 < n_mid; ++i) push(slab);
+  push(rem);
+  push(edge);
+  return n;
+}
+
+// Workspace of one slab's MLP call: slabs of different heights may take different paths (a last slab of
+// <= 64 rows takes the small-batch kernel with its own partial tiles), so the largest request counts.
+size_t host_slab_workspace_bytes(int64_t M, int64_t d, int64_t F) {
+  int64_t first[kMaxHostSlabs + 2], rows[kMaxHostSlabs + 2];
+  const int n = host_slab_plan(M, first, rows);
+  size_t bytes = 0;
+  for (int i = 0; i < n; ++i) bytes = std::max(bytes, fswiglu_workspace_bytes(rows[i], d, F));
   return round_up(bytes, 256);
 }
 
@@ -975,25 +1018,23 @@ int fswiglu_mlp_bf16_host(const void* x_host, const void* w_gate, const void* w_
   uint8_t* x_dev = static_cast<uint8_t*>(workspace);
   uint8_t* out_dev = x_dev + act;
   uint8_t* mlp_ws = out_dev + act;
-  const int64_t slab = host_slab_rows(M);
   const size_t mlp_ws_bytes = host_slab_workspace_bytes(M, d, F);
-  const int num_slabs = static_cast<int>((M + slab - 1) / slab);
+  int64_t slab_first[kMaxHostSlabs + 2], slab_rows[kMaxHostSlabs + 2];
+  const int num_slabs = host_slab_plan(M, slab_first, slab_rows);
   const size_t row_bytes = static_cast<size_t>(d) * 2u;
 
   bool ok = cudaEventRecord(st->ev_start, s) == cudaSuccess &&
             cudaStreamWaitEvent(st->h2d_stream, st->ev_start, 0) == cudaSuccess &&
             cudaStreamWaitEvent(st->d2h_stream, st->ev_start, 0) == cudaSuccess;
   for (int i = 0; i < num_slabs && ok; ++i) {
-    const int64_t r0 = i * slab;
-    const int64_t rows = (M - r0 < slab) ? (M - r0) : slab;
+    const int64_t r0 = slab_first[i], rows = slab_rows[i];
     ok = cudaMemcpyAsync(x_dev + r0 * row_bytes, static_cast<const uint8_t*>(x_host) + r0 * row_bytes,
                          rows * row_bytes, cudaMemcpyHostToDevice, st->h2d_stream) == cudaSuccess &&
          cudaEventRecord(st->ev_h2d[i], st->h2d_stream) == cudaSuccess;
   }
   int rc = FSWIGLU_OK;
   for (int i = 0; i < num_slabs && ok && rc == FSWIGLU_OK; ++i) {
-    const int64_t r0 = i * slab;
-    const int64_t rows = (M - r0 < slab) ? (M - r0) : slab;
+    const int64_t r0 = slab_first[i], rows = slab_rows[i];
     ok = cudaStreamWaitEvent(s, st->ev_h2d[i], 0) == cudaSuccess;
     if (!ok) break;
     rc = fswiglu_mlp_bf16(x_dev + r0 * row_bytes, d, w_gate, w_up, d, w_down, F, out_dev + r0 * row_bytes,

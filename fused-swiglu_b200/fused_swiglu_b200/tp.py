@@ -180,7 +180,7 @@ class TensorParallelSwiGLU:
         self.F_local, self.d = w_gate_shard.shape
         self._bufs = {}
         self._scratch = None
-        self._recv_hdl = self._out_hdl = None
+        self._recv_hdl = self._out_hdl = self._recv_bases = self._out_bases = None
         self._cuda = self.device.type == "cuda"
         self._comm_stream = torch.cuda.Stream(device=self.device, priority=-1) if self._cuda else None
         # reduce + broadcast kernel (push mode): 128 CTAs of 128 threads, one beside each GEMM CTA on most SMs.
@@ -290,7 +290,9 @@ class TensorParallelSwiGLU:
                 grp = self.group if self.group is not None else dist.group.WORLD
                 partial = symm_mem.empty((Mp, self.d), dtype=torch.bfloat16, device=dev)  # receive buffer
                 out = symm_mem.empty((Mp, self.d), dtype=torch.bfloat16, device=dev)
-                handles = (symm_mem.rendezvous(partial, grp), symm_mem.rendezvous(out, grp))
+                recv_hdl, out_hdl = symm_mem.rendezvous(partial, grp), symm_mem.rendezvous(out, grp)
+                # peer base addresses, read once: they are used for every launch of every step
+                handles = (recv_hdl, out_hdl, [int(p) for p in recv_hdl.buffer_ptrs], [int(p) for p in out_hdl.buffer_ptrs])
             else:
                 partial = torch.empty((Mp, self.d), dtype=self.wire_dtype, device=dev)
                 out = torch.empty((Mp, self.d), dtype=torch.bfloat16, device=dev)
@@ -307,7 +309,7 @@ class TensorParallelSwiGLU:
             self._bufs[key] = (partial, out, ws, handles)
         partial, out, ws, handles = self._bufs[key]
         if handles is not None:
-            self._recv_hdl, self._out_hdl = handles
+            self._recv_hdl, self._out_hdl, self._recv_bases, self._out_bases = handles
         return partial, out, ws
 
     def forward(self, x: torch.Tensor, slab_ready=None, slab_done=None, host_plan: bool = False) -> torch.Tensor:
@@ -467,8 +469,7 @@ class TensorParallelSwiGLU:
         lib, world, rank, d, Fl = capi.lib, self.world, self.rank, self.d, self.F_local
         compute = torch.cuda.current_stream(self.device)
         comm = self._comm_stream
-        recv_bases = [int(p) for p in self._recv_hdl.buffer_ptrs]
-        out_bases = [int(p) for p in self._out_hdl.buffer_ptrs]
+        recv_bases, out_bases = self._recv_bases, self._out_bases
         PtrArr = ctypes.c_void_p * world
         vp = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
         off = 0

@@ -344,8 +344,12 @@ def test_raw_op_writes_half_width_rows_into_full_width_buffer(fsw, cuda_dev):
     assert bool((C.flatten()[M * N // 2:] == 7.0).all())
 
 
-def test_host_buffer_entry_point(fsw, cuda_dev):
-    M, d, F = 2500, 256, 520
+@pytest.mark.parametrize("M", [2500, 1030, 4096, 4097, 5000, 8200])
+def test_host_buffer_entry_point(fsw, cuda_dev, M):
+    """Activations in pinned host memory, row slabs pipelined over copy streams.  2500 / 1030: equal slabs with a
+    ragged (1030: six-row, small-batch kernel) last one; from 4096 rows the first and last slab are half as tall,
+    4097 and 5000 leave a remainder for the slab before the last; from 8192 rows the middle slabs are 2048 rows tall."""
+    d, F = 256, 520
     x, wg, wu, wd = fsw.inputs.make_mlp_inputs(M, d, F, seed=8)
     wg, wu, wd = wg.to(cuda_dev), wu.to(cuda_dev), wd.to(cuda_dev)
     xh = x.pin_memory()
