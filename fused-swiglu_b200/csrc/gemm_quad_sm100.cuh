@@ -23,7 +23,9 @@
 // at the same time and release them separately.  The MMA issuer starts the next tile with the sub-tile-0 MMAs
 // of the first k-blocks (as many as the ring has stages) as soon as accumulator 0 is free, then waits for
 // accumulator 1, issues the sub-tile-1 MMAs of those k-blocks and releases their stages; from there on both
-// sub-tiles go k-block by k-block.
+// sub-tiles go k-block by k-block - except for the last three k-blocks of the tile, where sub-tile 0 is finished
+// first (its accumulator is handed to its epilogue group while sub-tile 1's last MMAs still run).  Each
+// accumulator has its own "full" barrier.
 #pragma once
 
 #include "gemm_common.cuh"
@@ -46,15 +48,15 @@ gemm_quad_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_base + kQuadStages * kQuadStageBytes;
-  // barrier block: full[4], empty[4], tmem_full, tmem_empty[2], drain, then bookkeeping words
+  // barrier block: full[4], empty[4], tmem_full[2], tmem_empty[2], drain, then bookkeeping words
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kQuadStages + s); };
-  const uint32_t tfull_bar = bar_base + 8u * (2 * kQuadStages);
-  auto tempty_bar = [&](int h) { return bar_base + 8u * (2 * kQuadStages + 1 + h); };
-  const uint32_t drain_bar = bar_base + 8u * (2 * kQuadStages + 3);
+  auto tfull_bar = [&](int h) { return bar_base + 8u * (2 * kQuadStages + h); };
+  auto tempty_bar = [&](int h) { return bar_base + 8u * (2 * kQuadStages + 2 + h); };
+  const uint32_t drain_bar = bar_base + 8u * (2 * kQuadStages + 4);
   uint8_t* generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
   volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(
-      generic_base + kQuadStages * kQuadStageBytes + 8 * (2 * kQuadStages + 4));
+      generic_base + kQuadStages * kQuadStageBytes + 8 * (2 * kQuadStages + 5));
   volatile uint32_t* abort_flag = tmem_ptr_slot + 1;
   volatile uint32_t* epi_ok = tmem_ptr_slot + 2;  // two entries per epilogue group, alternating per tile
 
@@ -68,7 +70,8 @@ gemm_quad_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    mbar_init(tfull_bar, 1);
+    mbar_init(tfull_bar(0), 1);
+    mbar_init(tfull_bar(1), 1);
     mbar_init(tempty_bar(0), 8);  // 4 epilogue warps in each of the two CTAs
     mbar_init(tempty_bar(1), 8);
     mbar_init(drain_bar, 1);
@@ -227,7 +230,10 @@ gemm_quad_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             phase ^= 1u;
           }
         }
-        for (int kb = lead; kb < num_kb; ++kb) {
+        // the last k-blocks of the tile (as many as fit in the ring beside one stage for the producer): sub-tile 0
+        // first, so that its accumulator reaches its epilogue group while sub-tile 1's last MMAs still run
+        const int trail = max(0, min(kQuadStages - 1, num_kb - lead));
+        for (int kb = lead; kb < num_kb - trail; ++kb) {
           if (!wd.wait<true>(full_bar(stage), phase, kSiteMmaFull)) {
             alive = false;
             break;
@@ -242,7 +248,33 @@ gemm_quad_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           }
         }
         if (!alive) break;
-        umma_commit_pair(tfull_bar);  // both accumulators complete, in both CTAs
+        {
+          int s = stage;
+          uint32_t ph = phase;
+          for (int j = 0; j < trail; ++j) {
+            if (!wd.wait<true>(full_bar(s), ph, kSiteMmaFull)) {
+              alive = false;
+              break;
+            }
+            tc_fence_after_sync();
+            issue(s, 0, d0, false);
+            if (++s == kQuadStages) {
+              s = 0;
+              ph ^= 1u;
+            }
+          }
+        }
+        if (!alive) break;
+        umma_commit_pair(tfull_bar(0));  // accumulator 0 complete, in both CTAs
+        for (int j = 0; j < trail; ++j) {
+          issue(stage, 1, d1, false);
+          umma_commit_pair(empty_bar(stage));
+          if (++stage == kQuadStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        umma_commit_pair(tfull_bar(1));  // accumulator 1 complete
         acc_phase ^= 1u;
       }
       if (wd.aborted()) {
@@ -271,7 +303,7 @@ gemm_quad_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const TileCoord tc = tile_coord(tile, p);
       // One thread of the group waits for the accumulators and tells the other 127: the four warps share a
       // named barrier, so they must all take the same exit if a wait gives up.
-      if (group_tid == 0) ok_slot[iter & 1u] = wd.wait(tfull_bar, acc_phase, kSiteEpilogueFull) ? 1u : 0u;
+      if (group_tid == 0) ok_slot[iter & 1u] = wd.wait(tfull_bar(group), acc_phase, kSiteEpilogueFull) ? 1u : 0u;
       if (group == 0) {
         asm volatile("bar.sync 1, 128;" ::: "memory");
       } else {
