@@ -21,6 +21,7 @@ exercised with CPU ranks over gloo.
 """
 from __future__ import annotations
 
+import os
 from typing import Callable, Optional
 
 import torch
@@ -424,6 +425,22 @@ class TensorParallelSwiGLU:
             peers = [hdl.get_buffer(p, (M, self.d), torch.bfloat16) for p in range(world)]
             self._xin = (xin, hdl, peers)
         xin, hdl, peers = self._xin
+        if os.environ.get("FSWIGLU_TP_HOST_PIPELINE", "1") == "0":
+            # the plain order, for comparison: everything in, all slabs, everything out
+            for g0, g1 in owned:
+                if g1 > g0:
+                    xin[g0:g1].copy_(x_host[g0:g1], non_blocking=True)
+                    for k in range(1, world):
+                        peers[(rank + k) % world][g0:g1].copy_(xin[g0:g1], non_blocking=True)
+            hdl.barrier(channel=14)
+            out = self.forward(xin, host_plan=True)
+            o = 0
+            for g0, g1 in owned:
+                out_host[o:o + g1 - g0].copy_(out[g0:g1], non_blocking=True)
+                o += g1 - g0
+            hdl.barrier(channel=15)
+            torch.cuda.current_stream(self.device).synchronize()
+            return
         if self._copy_streams is None:
             self._copy_streams = (torch.cuda.Stream(device=self.device), torch.cuda.Stream(device=self.device))
         h2d, d2h = self._copy_streams

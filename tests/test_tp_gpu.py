@@ -84,10 +84,12 @@ def _worker(rank, world, port, mode, M, q):
         owned = tp.owned_rows(M)
         want = torch.cat([out[g0:g1] for g0, g1 in owned]).cpu()
         x_pinned = x.pin_memory()
-        for _ in range(2):
+        for pipeline in ("1", "1", "0"):  # slab-wise copies beside the GEMMs (twice), then the plain order
+            os.environ["FSWIGLU_TP_HOST_PIPELINE"] = pipeline
             out_host = torch.zeros((want.size(0), out.size(1)), dtype=torch.bfloat16).pin_memory()
             tp.forward_from_host(x_pinned, out_host)
             same = same and torch.equal(out_host, want)
+        os.environ.pop("FSWIGLU_TP_HOST_PIPELINE", None)
         counts = [torch.zeros(1, dtype=torch.int64, device=dev) for _ in range(world)]
         dist.all_gather(counts, torch.tensor([want.size(0)], dtype=torch.int64, device=dev))
         same = same and sum(int(c.item()) for c in counts) == M  # the ranks' rows cover the result exactly once
