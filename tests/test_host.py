@@ -106,7 +106,7 @@ def test_seeded_inputs_are_deterministic_and_shaped():
     assert not torch.equal(a[0], c[0])
 
 
-def test_ragged_batch_length_matches_survey_value():
+def test_ragged_batch_length_is_the_configured_32414_rows():
     assert int(inputs.ragged_lengths(0).sum()) == 32414
     assert 32414 % 128 == 30
 
