@@ -45,7 +45,7 @@ def _run(cmd: list[str], verbose: bool) -> None:
 
 
 def lib_sources() -> list[str]:
-    files = [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC)) if f.endswith((".cu", ".cuh"))]
+    files = [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC)) if f.endswith((".cu", ".cuh", ".h"))]
     files.append(os.path.join(os.path.dirname(HERE), "include", "fswiglu.h"))
     return files
 

@@ -219,6 +219,19 @@ def test_pair_kernel_schedule_arithmetic(tmp_path):
     assert res.returncode == 0 and res.stdout.startswith("ok "), res.stdout[-400:]
 
 
+def test_host_pipeline_slab_plan(tmp_path):
+    """The row slabs of the host-buffer pipeline (csrc/host_slabs.h) for every batch size up to 70 000 rows and
+    a sweep beyond: contiguous, non-empty, covering, never more than the pipeline has events for."""
+    import subprocess
+
+    exe = tmp_path / "check_host_slabs"
+    src = os.path.join(ROOT, "tests", "native", "check_host_slabs.cpp")
+    inc = os.path.join(ROOT, "fused-swiglu_b200", "csrc")
+    subprocess.run(["g++", "-O1", "-std=c++17", f"-I{inc}", src, "-o", str(exe)], check=True)
+    res = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0 and res.stdout.startswith("ok "), res.stdout[-400:]
+
+
 def test_graph_capture_traces_through_the_ops():
     """torch.compile(fullgraph=True) must trace the module and the alias-annotated launcher without a graph
     break; on a CPU-only machine the captured graph then fails at run time, with the dispatcher's missing
