@@ -130,6 +130,21 @@ def test_tp_slab_bounds_cover_rows():
             assert len(b) <= 4
 
 
+def test_host_slab_planner_properties():
+    """The planner of the host-buffer step: same structural guarantees as the device-resident one, and it never
+    prefers fewer slabs than that one (the exposed copies only add to the cost of tall first and last slabs)."""
+    from fused_swiglu_b200.tp import _host_timeline_us, plan_host_slabs, plan_slabs
+
+    for (M, d, Fl, world) in [(8192, 8192, 3584, 8), (8192, 8192, 14336, 2), (32414, 5120, 1728, 8), (32414, 5120, 6912, 2),
+                              (4096, 4096, 5504, 2), (1000, 4096, 1376, 8), (1, 64, 8, 2)]:
+        rows = plan_host_slabs(M, d, Fl, world, 148)
+        assert sum(rows) == M and all(r > 0 for r in rows) and len(rows) <= 8
+        assert all(r % (8 * world) == 0 for r in rows[:-1])
+        dev_rows = plan_slabs(M, d, Fl, world, 148)
+        assert len(rows) >= len(dev_rows)
+        assert _host_timeline_us(rows, d, Fl, world, 148) <= _host_timeline_us(dev_rows, d, Fl, world, 148) + 1e-9
+
+
 def test_slab_planner_properties():
     from fused_swiglu_b200.tp import plan_slabs
 
