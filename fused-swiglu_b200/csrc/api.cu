@@ -553,11 +553,39 @@ int launch_gemm_quad(const DeviceState& st, const void* a, int64_t lda, const vo
   return cudaGetLastError() == cudaSuccess ? FSWIGLU_OK : FSWIGLU_ERR_CUDA;
 }
 
+// Very tall problems are run as row slabs of about 8192 rows, one launch each (rows are independent, results
+// are bit-identical).  Measured at K = 8192, F = 28672 in 0.5 s loops: 65536 rows in one launch 1153-1217 TF/s
+// (gate-up) / 1114-1128 (down), in slabs of 16384 rows 1295 / 1330, of 8192 rows 1345 / 1375, of 4096 rows
+// 1328 / 1321; 32414 rows: 1245-1281 / 1197-1217 in one launch, 1331 / 1364 in slabs of 8192.  The per-wave
+// operand sets are the same in all of them; what grows with M is the memory the launch walks over.
+// FSWIGLU_TALL_SLAB=<rows> changes the slab height, 0 turns the slabs off (experiments, tests).
+int64_t tall_slab_rows(int64_t M) {
+  int64_t target = 8192;
+  if (const char* env = std::getenv("FSWIGLU_TALL_SLAB")) {
+    const long v = std::atol(env);
+    if (v == 0) return M;
+    if (v >= 512) target = v;
+  }
+  if (M <= target + target / 2) return M;
+  const int64_t n = (M + target - 1) / target;
+  return ((M + n - 1) / n + 511) / 512 * 512;  // equal slabs, whole 512-row tiles
+}
+
 int gateup_impl(DeviceState& st, const void* x, int64_t ldx, const void* w0, int64_t ldw,
                 const void* w_up, void* h, int64_t ldh, int64_t M, int64_t F, int64_t d,
                 int interleaved, const float* row_scale, const Scratch& scratch, cudaStream_t stream) {
   int rc;
   if (M == 0) return FSWIGLU_OK;  // empty batch: nothing to read or write, pointers may be null
+  if (const int64_t slab = tall_slab_rows(M); slab < M) {
+    for (int64_t r0 = 0; r0 < M; r0 += slab) {
+      const int64_t rows = std::min(slab, M - r0);
+      rc = gateup_impl(st, static_cast<const uint8_t*>(x) + r0 * ldx * 2, ldx, w0, ldw, w_up,
+                       static_cast<uint8_t*>(h) + r0 * ldh * 2, ldh, rows, F, d, interleaved,
+                       row_scale != nullptr ? row_scale + r0 : nullptr, scratch, stream);
+      if (rc != FSWIGLU_OK) return rc;
+    }
+    return FSWIGLU_OK;
+  }
   if ((rc = check_matrix(x, M, d, ldx, true))) return rc;
   if (interleaved) {
     if (w_up != nullptr) return FSWIGLU_ERR_BAD_ARG;
@@ -620,6 +648,18 @@ int down_impl(DeviceState& st, const void* h, int64_t ldh, const void* w_down, i
   int rc;
   if (out_dtype != FSWIGLU_OUT_BF16 && out_dtype != FSWIGLU_OUT_F32) return FSWIGLU_ERR_BAD_ARG;
   if (M == 0) return FSWIGLU_OK;
+  if (const int64_t slab = tall_slab_rows(M); slab < M) {  // very tall: row slabs, one launch each
+    const int64_t out_bytes = out_dtype == FSWIGLU_OUT_F32 ? 4 : 2;
+    for (int64_t r0 = 0; r0 < M; r0 += slab) {
+      const int64_t rows = std::min(slab, M - r0);
+      rc = down_impl(st, static_cast<const uint8_t*>(h) + r0 * ldh * 2, ldh, w_down, ldw,
+                     static_cast<uint8_t*>(out) + r0 * ldo * out_bytes, ldo, rows, d, F, out_dtype,
+                     residual != nullptr ? static_cast<const uint8_t*>(residual) + r0 * ldr * 2 : nullptr, ldr,
+                     scratch, stream);
+      if (rc != FSWIGLU_OK) return rc;
+    }
+    return FSWIGLU_OK;
+  }
   if ((rc = check_matrix(h, M, F, ldh, true))) return rc;
   if ((rc = check_matrix(w_down, d, F, ldw, true))) return rc;
   if ((rc = check_matrix(out, M, d, ldo, false))) return rc;
@@ -1376,6 +1416,7 @@ int fswiglu_plan_kernel(int64_t M, int64_t n_out, int64_t K, int gated) {
   if (M < 0 || n_out <= 0 || K <= 0) return FSWIGLU_ERR_SHAPE;
   DeviceState* st = nullptr;
   if (int rc = device_state(&st)) return rc;
+  M = std::min(M, tall_slab_rows(M));  // very tall problems run as row slabs: the plan is that of one slab
   GemmParams p = {};
   p.M = static_cast<int>(M);
   p.n_out = static_cast<int>(n_out);

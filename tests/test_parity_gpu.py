@@ -168,6 +168,40 @@ def test_small_batch_reduction_paths_agree_bitwise(fsw, cuda_dev, M, d, F):
     assert m["rel_fro"] <= REL_FRO_GRADED and m["scaled_max_abs"] <= SCALED_MAX_ABS, m
 
 
+def test_very_tall_problems_run_as_row_slabs_with_identical_results(fsw, cuda_dev):
+    """Above 12288 rows the tiled GEMMs are launched slab by slab (about 8192 rows each); rows are independent,
+    so the result must equal the single-launch result bit for bit, with every option."""
+    M, d, F = 20011, 256, 520
+    x, wg, wu, wd = (t.to(cuda_dev) for t in fsw.inputs.make_mlp_inputs(M, d, F, seed=17))
+    scale = (0.5 + torch.rand((M,), generator=torch.Generator().manual_seed(3))).to(cuda_dev)
+    res = torch.randn((M, d), generator=torch.Generator().manual_seed(4)).to(torch.bfloat16).to(cuda_dev)
+    outs = {}
+    for mode in ("0", None):
+        old = os.environ.get("FSWIGLU_TALL_SLAB")
+        if mode is None:
+            os.environ.pop("FSWIGLU_TALL_SLAB", None)
+        else:
+            os.environ["FSWIGLU_TALL_SLAB"] = mode
+        try:
+            before = fsw.capi.launch_count()
+            plain = fsw.ops.fused_swiglu_mlp_bf16(x, wg, wu, wd)
+            launches = fsw.capi.launch_count() - before
+            outs[mode] = (plain, fsw.ops.fused_swiglu_mlp_bf16(x, wg, wu, wd, residual=res, row_scale=scale),
+                          fsw.ops.fused_swiglu_mlp_bf16(x, wg, wu, wd, out_dtype=torch.float32), launches)
+            healthy(fsw)
+        finally:
+            if old is None:
+                os.environ.pop("FSWIGLU_TALL_SLAB", None)
+            else:
+                os.environ["FSWIGLU_TALL_SLAB"] = old
+    assert outs["0"][3] == 2 and outs[None][3] == 6  # one launch per GEMM; three slabs per GEMM
+    for a, b in zip(outs["0"][:3], outs[None][:3]):
+        assert torch.equal(a, b)
+    rows = [0, 7167, 7168, 14335, 14336, 20010]  # the slab edges (slabs of 7168, 7168 and 5675 rows)
+    m = orc.error_metrics(f32(outs[None][0][rows]), orc.mlp_fp32(*[f32(t) for t in (x[rows], wg, wu, wd)]))
+    assert m["rel_fro"] <= REL_FRO_GRADED and m["scaled_max_abs"] <= SCALED_MAX_ABS, m
+
+
 # ------------------------------------------------------------------ the benchmark configurations
 def test_config1_full_size_within_published_tolerance(fsw, cuda_dev):
     """Configuration 1 (M=512, d=1024, F=2816): whole output vs the fp32 expression,
